@@ -252,7 +252,8 @@ typedef struct {
   int32_t enable_chunked_prefill; /* vllm --enable-chunked-prefill                        */
   int32_t device;                 /* CUDA device ordinal                                   */
   int32_t dtype;                  /* vllm --dtype: 0 auto (config.json torch_dtype: float16 -> float16, else bfloat16),
-                                     1 bfloat16, 2 float16 (ref:values-01-minimal-example8.yaml:30-31)                  */
+                                     1 bfloat16, 2 float16 (ref:values-01-minimal-example8.yaml:30-31), 3 float32 (storage
+                                     and arithmetic in true 32-bit; layer-list models only)                             */
 } kge_engine_config;
 
 /* One engine step's device-side metadata - what vLLM hands its attention backend
@@ -268,6 +269,8 @@ typedef struct {
   const int64_t* slot_mapping;    /* [T]   */
   const int32_t* logits_rows;     /* [R] rows of the flattened batch that need logits */
   int32_t R;
+  const int32_t* state_slots;     /* [B] models with recurrent state: each request's slot of the state pool (< max_num_seqs);
+                                     NULL = request i uses slot i.  A request whose first row is position 0 starts from zero. */
 } kge_step_batch;
 
 /* Load an HF-layout directory (config.json + *.safetensors), the same thing the values
@@ -457,6 +460,21 @@ int kge_engine_step(kge_engine* e, kge_step_output* outs, int32_t cap);
  * cap >= sum of max_tokens + number of requests is always enough.  Returns 0 or a negative error. */
 int kge_engine_run_to_completion(kge_engine* e, kge_step_output* events, int64_t cap, int64_t* n_events,
                                  int32_t* n_steps);
+/* Trace replay (no counterpart in the reference): a recorded sequence of steps is fed through the engine's own
+ * scheduler objects, block pool, state slots and forward pass, and the logits of chosen rows come back in fp32.  Nothing
+ * is sampled.  kge_trace_add registers a request with its first tokens, or appends tokens to a known one; kge_trace_step
+ * runs exactly num_tokens[i] further tokens of request request_ids[i] for every i as ONE batch (prompt pieces beside
+ * single tokens) and writes the logits of the places want[want_start[i] .. want_start[i+1]) (indices among that
+ * request's tokens of this step) to out_logits_host, [sum of wants, vocab], in order; kge_trace_end gives a request's
+ * blocks and state slot back.  Fails, changing nothing, when the pool has too few blocks or slots for the step. */
+int kge_trace_add(kge_engine* e, int64_t request_id, const int32_t* token_ids, int32_t n);
+int kge_trace_step(kge_engine* e, const int64_t* request_ids, const int32_t* num_tokens, int32_t n,
+                   const int32_t* want_start, const int32_t* want, float* out_logits_host);
+int kge_trace_end(kge_engine* e, int64_t request_id);
+/* Diagnostics for layer-list models: while host_buffer is non-null, every step copies the fp32 residual stream after
+ * each layer to host_buffer[layer][row][width] (rows of the step's flattened batch), as far as capacity_floats reaches. */
+int kge_engine_set_layer_dump(kge_engine* e, float* host_buffer, int64_t capacity_floats);
+
 /* Counters for /metrics (vllm:v1/metrics/loggers.py:452-788). */
 int kge_engine_stats(const kge_engine* e, int32_t* num_running, int32_t* num_waiting,
                      float* kv_usage, int64_t* num_preemptions);

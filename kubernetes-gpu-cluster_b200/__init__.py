@@ -34,7 +34,7 @@ class StepBatch(C.Structure):
     _fields_ = [("T", C.c_int32), ("B", C.c_int32), ("token_ids", C.c_void_p), ("positions", C.c_void_p),
                 ("query_start_loc", C.c_void_p), ("seq_lens", C.c_void_p), ("block_table", C.c_void_p),
                 ("max_blocks", C.c_int32), ("slot_mapping", C.c_void_p), ("logits_rows", C.c_void_p),
-                ("R", C.c_int32)]
+                ("R", C.c_int32), ("state_slots", C.c_void_p)]
 
 
 class CSamplingParams(C.Structure):
@@ -154,6 +154,10 @@ SIGNATURES = {
     "kge_sched_schedule": (_I, [_P, _P, _P, C.c_int32]),
     "kge_sched_update": (_I, [_P, _P, _P, C.c_int32, C.POINTER(StepOutput), C.c_int32]),
     "kge_sched_counts": (_I, [_P, _P, _P, _P]),
+    "kge_trace_add": (_I, [_P, _L, _P, C.c_int32]),
+    "kge_trace_step": (_I, [_P, _P, _P, C.c_int32, _P, _P, _P]),
+    "kge_trace_end": (_I, [_P, _L]),
+    "kge_engine_set_layer_dump": (_I, [_P, _P, _L]),
 }
 
 # float16 twins of the element-type dependent ops: same signatures (include/kge.h)
@@ -166,7 +170,7 @@ for _n, _t in {"kge_embed": "kge_embed_f16", "kge_rmsnorm": "kge_rmsnorm_f16", "
                "kge_logprobs": "kge_logprobs_f16", "kge_tp_reduce_add_norm": "kge_tp_reduce_add_norm_f16"}.items():
     SIGNATURES[_t] = SIGNATURES[_n]
 
-DTYPES = {"auto": 0, "bfloat16": 1, "float16": 2, "half": 2}
+DTYPES = {"auto": 0, "bfloat16": 1, "float16": 2, "half": 2, "float32": 3}
 _lib = None
 
 
@@ -297,7 +301,8 @@ class LLM:
                  enable_prefix_caching: bool = True, dtype: str = "auto"):
         require_cuda()
         if dtype not in DTYPES:
-            raise KgeError(f"dtype {dtype!r}: this engine computes in bfloat16 or float16 (auto, bfloat16, float16)")
+            raise KgeError(f"dtype {dtype!r}: this engine computes in bfloat16 or float16, layer-list models also in float32 "
+                           "(auto, bfloat16, float16, float32)")
         self.cfg = EngineConfig(max_num_seqs, max_num_batched_tokens, max_model_len, block_size,
                                 num_gpu_blocks_override, gpu_memory_utilization, tp_rank,
                                 tensor_parallel_size, int(enable_chunked_prefill), device, DTYPES[dtype])
@@ -322,7 +327,7 @@ class LLM:
     @property
     def dtype(self) -> str:
         """What the engine computes in: "bfloat16" or "float16" (what `dtype="auto"` settled on)."""
-        return {1: "bfloat16", 2: "float16"}.get(lib().kge_engine_dtype(self._h), "?")
+        return {1: "bfloat16", 2: "float16", 3: "float32"}.get(lib().kge_engine_dtype(self._h), "?")
 
     @property
     def num_gpu_blocks(self) -> int:
@@ -442,6 +447,37 @@ class LLM:
             d.setdefault(ids[k], Logprob(vals[k], k))
         return d
 
+    # trace replay: scripted steps through the scheduler's pools and the forward pass, logits out, nothing sampled
+    def trace_add(self, rid: int, token_ids):
+        """Register request `rid` with its first tokens, or append tokens to it."""
+        import numpy as np
+        arr = np.ascontiguousarray(token_ids, dtype=np.int32)
+        check(lib().kge_trace_add(self._h, rid, arr.ctypes.data, int(arr.size)), "kge_trace_add")
+
+    def trace_step(self, entries):
+        """entries: [(rid, number of further tokens to run, [places among them whose logits are wanted])], run as one
+        batch.  Returns the wanted logits, float32 [sum of wants, vocab], in order."""
+        import numpy as np
+        ids = np.asarray([e[0] for e in entries], dtype=np.int64)
+        cnt = np.asarray([e[1] for e in entries], dtype=np.int32)
+        ws = np.zeros(len(entries) + 1, dtype=np.int32)
+        ws[1:] = np.cumsum([len(e[2]) for e in entries])
+        want = np.asarray([w for e in entries for w in e[2]] or [0], dtype=np.int32)
+        out = np.zeros((int(ws[-1]), self.vocab_size), dtype=np.float32)
+        check(lib().kge_trace_step(self._h, ids.ctypes.data, cnt.ctypes.data, len(entries), ws.ctypes.data, want.ctypes.data,
+                                   out.ctypes.data if ws[-1] else None), "kge_trace_step")
+        return out
+
+    def trace_end(self, rid: int):
+        check(lib().kge_trace_end(self._h, rid), "kge_trace_end")
+
+    def set_layer_dump(self, buf):
+        """Diagnostics (layer-list models): a float32 numpy array that receives the residual stream after every layer of
+        the following steps, [layer, row, width]; None switches it off."""
+        self._dump = buf
+        check(lib().kge_engine_set_layer_dump(self._h, buf.ctypes.data if buf is not None else None, int(buf.size) if buf is not None else 0),
+              "kge_engine_set_layer_dump")
+
     def step(self):
         """One engine step (schedule + forward + sample + update).  Returns a list of
         (request_id, token or -1, finished 0|1|2, num_scheduled)."""
@@ -537,7 +573,7 @@ class LLM:
         tid, pos, qsl = a(token_ids, np.int32), a(positions, np.int32), a(query_start_loc, np.int32)
         sl, bt, sm, rows = a(seq_lens, np.int32), a(block_table, np.int32), a(slot_mapping, np.int64), a(logits_rows, np.int32)
         b = StepBatch(len(tid), len(sl), tid.ctypes.data, pos.ctypes.data, qsl.ctypes.data, sl.ctypes.data,
-                      bt.ctypes.data, max_blocks, sm.ctypes.data, rows.ctypes.data, len(rows))
+                      bt.ctypes.data, max_blocks, sm.ctypes.data, rows.ctypes.data, len(rows), None)
         out = np.zeros(max(1, len(rows)), dtype=np.int32)
         lg = np.zeros((len(rows), self.vocab_size), dtype=np.float32) if want_logits else None
         check(lib().kge_step(self._h, C.byref(b), out.ctypes.data, lg.ctypes.data if want_logits else None), "kge_step")

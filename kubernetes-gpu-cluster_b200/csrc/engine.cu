@@ -39,6 +39,13 @@ __global__ void fill_const_kernel(bf16* p, int64_t n, float v, bool f16) {
     reinterpret_cast<uint16_t*>(p)[i] = to_elt_bits(v, f16);
 }
 
+void fill_uniform(void* p, int64_t n, uint64_t seed, float scale, bool f16, cudaStream_t st) {
+  if (n > 0) fill_uniform_kernel<<<(int)std::min<int64_t>((n + 255) / 256, 148 * 8), 256, 0, st>>>((bf16*)p, n, seed, scale, f16);
+}
+void fill_const(void* p, int64_t n, float v, bool f16, cudaStream_t st) {
+  if (n > 0) fill_const_kernel<<<(int)std::min<int64_t>((n + 255) / 256, 148 * 8), 256, 0, st>>>((bf16*)p, n, v, f16);
+}
+
 struct Builder {
   kge_engine* e;
   const ModelDir* md;
@@ -294,6 +301,8 @@ StepMeta carve_meta(uint8_t* base, int T, int B, int R, int max_blocks, int64_t*
   m.temp = (float*)take((int64_t)R * 4);
   m.top_p = (float*)take((int64_t)R * 4);
   m.btab = (int32_t*)take((int64_t)B * max_blocks * 4);
+  m.sslot = (int32_t*)take((int64_t)B * 4);
+  m.treq = (int32_t*)take((int64_t)T * 4);
   if (total) *total = off;
   return m;
 }
@@ -328,17 +337,22 @@ extern "C" int kge_engine_create(kge_engine** out, const char* model_dir, const 
   const ModelSpec& s = e->spec;
   if (!md.has_weights() && dummy_seed < 0) ENGINE_FAIL("kge_engine_create: no *.safetensors in %s (use --load-format dummy)", model_dir);
   // --dtype: auto follows the checkpoint (float16 stays float16; everything else runs in bfloat16), or as told
-  if (cfg->dtype < 0 || cfg->dtype > 2) ENGINE_FAIL("kge_engine_create: dtype %d (0 auto, 1 bfloat16, 2 float16)", cfg->dtype);
+  if (cfg->dtype < 0 || cfg->dtype > 3) ENGINE_FAIL("kge_engine_create: dtype %d (0 auto, 1 bfloat16, 2 float16, 3 float32)", cfg->dtype);
+  if (cfg->dtype == 3 && !s.is_hybrid()) ENGINE_FAIL("kge_engine_create: float32 is implemented for layer-list models only; %s runs in bfloat16 or float16", s.model_type.c_str());
+  if (cfg->dtype == 2 && s.is_hybrid()) ENGINE_FAIL("kge_engine_create: %s runs in bfloat16 or float32", s.model_type.c_str());
+  e->f32 = cfg->dtype == 3;
   e->f16 = cfg->dtype == 2 || (cfg->dtype == 0 && (s.torch_dtype == "float16" || s.torch_dtype == "half"));
   e->op = e->f16 ? &kOpsF16 : &kOpsBf16;
   e->tp_size = cfg->tp_size > 0 ? cfg->tp_size : 1;
   e->tp_rank = cfg->tp_rank;
   if (e->tp_rank < 0 || e->tp_rank >= e->tp_size) ENGINE_FAIL("kge_engine_create: tp_rank %d of %d", e->tp_rank, e->tp_size);
+  if (!s.is_hybrid()) {
   if (s.H % e->tp_size || s.ffn % e->tp_size) ENGINE_FAIL("kge_engine_create: heads %d / ffn %d not divisible by tensor-parallel-size %d", s.H, s.ffn, e->tp_size);
   if (e->tp_size > s.KV && e->tp_size % s.KV) ENGINE_FAIL("kge_engine_create: tensor-parallel-size %d incompatible with %d kv heads", e->tp_size, s.KV);
   e->H_loc = s.H / e->tp_size;
   e->KV_loc = std::max(1, s.KV / e->tp_size);
   e->ffn_loc = s.ffn / e->tp_size;
+  }
   // vocabulary shard of the LM head: equal widths, a multiple of 8 so gathered rows move as 16-byte vectors
   e->vocab_shard = e->tp_size == 1 ? s.vocab : ((s.vocab + e->tp_size - 1) / e->tp_size + 7) / 8 * 8;
   e->vocab_col0 = e->tp_rank * e->vocab_shard;
@@ -364,6 +378,13 @@ extern "C" int kge_engine_create(kge_engine** out, const char* model_dir, const 
   if (e->cfg.gpu_memory_utilization <= 0.f) e->cfg.gpu_memory_utilization = 0.9f;
   if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) ENGINE_FAIL("cudaStreamCreate failed");
 
+  if (s.is_hybrid()) {
+    if (e->tp_size > 1) ENGINE_FAIL("kge_engine_create: %s runs on one GPU (tensor-parallel-size 1)", s.model_type.c_str());
+    std::string herr;
+    if (hybrid_engine_build(e, md, dummy_seed, &herr)) ENGINE_FAIL("kge_engine_create: %s", herr.c_str());
+    *out = e;
+    return 0;
+  }
   Builder b{e, &md, dummy_seed};
   const bool ok = s.is_opt() ? build_opt(b) : build_llama(b);
   if (!ok) ENGINE_FAIL("kge_engine_create: %s", b.err.c_str());
@@ -494,7 +515,7 @@ extern "C" void kge_engine_destroy(kge_engine* e) {
 }
 
 extern "C" int kge_engine_num_blocks(const kge_engine* e) { return e ? e->num_blocks : 0; }
-extern "C" int kge_engine_dtype(const kge_engine* e) { return e ? (e->f16 ? 2 : 1) : 0; }
+extern "C" int kge_engine_dtype(const kge_engine* e) { return e ? (e->f32 ? 3 : e->f16 ? 2 : 1) : 0; }
 extern "C" int kge_engine_vocab(const kge_engine* e) { return e ? e->spec.vocab : 0; }
 extern "C" int kge_engine_eos_token_id(const kge_engine* e) { return e ? e->spec.eos : -1; }
 extern "C" int kge_engine_max_model_len(const kge_engine* e) { return e ? e->cfg.max_model_len : 0; }

@@ -49,6 +49,26 @@ struct LayerW {
   bf16 *q_norm = nullptr, *k_norm = nullptr;   // qwen3: [hd] each
 };
 
+// Weights of one layer of a layer-list ("hybrid") model, in the engine's storage type (bfloat16 or float32).
+struct HybMat { void* w = nullptr; void* b = nullptr; int N = 0, K = 0; };
+struct HybridLayerW {
+  void* norm1 = nullptr;
+  // gated linear recurrence: [y | x] projection with bias, conv, block-diagonal gate projections, decay parameter, output
+  HybMat yx, o, ra, ri;
+  void *conv_w = nullptr, *conv_b = nullptr, *lam = nullptr;
+  // parallel mixer: one projection [q | k | v | mq | mk | mv | mg] for both sides (column offsets below), the matrix
+  // memory's gate projection (fp32 output: rows i then f), its output norm, and ONE output projection over the
+  // concatenated [attention | matrix memory] activations (the two sides' scales are applied to the activations)
+  HybMat proj, gates, o2;
+  int off_k = 0, off_v = 0, off_mq = 0, off_mk = 0, off_mv = 0, off_mg = 0;
+  void* m_norm = nullptr;
+  void *kc = nullptr, *vc = nullptr;          // paged caches of the attention side
+  // feed-forward: dense (up, down) or experts ([E, ff, d] gate and up, [E, d, ff] down) + router (+ shared expert)
+  HybMat up, down, router, s_gate, s_up, s_down;
+  void *e_gate = nullptr, *e_up = nullptr, *e_down = nullptr;
+  int64_t state_off = 0;                      // floats from the start of a state slot to this layer's state
+};
+
 // Per-step metadata, laid out once in pinned host memory and mirrored on the device with the
 // same offsets so one cudaMemcpyAsync moves everything.
 struct StepMeta {
@@ -56,6 +76,7 @@ struct StepMeta {
   int64_t* slots;
   float *temp, *top_p;
   uint64_t* seeds;
+  int32_t *sslot, *treq;      // models with recurrent state: state slot of every request [B]; request index of every row [T]
 };
 
 }  // namespace kge
@@ -65,6 +86,17 @@ struct kge_engine {
   kge_engine_config cfg;
   int tp_rank = 0, tp_size = 1;
   bool f16 = false;                          // float16 model (--dtype float16); bfloat16 otherwise
+  bool f32 = false;                          // float32 storage and arithmetic (--dtype float32; layer-list models only)
+  // layer-list ("hybrid") models: fp32 residual stream, their own activation arena and the recurrent-state pool
+  std::vector<kge::HybridLayerW> hyb;
+  float *res32 = nullptr, *gates32 = nullptr, *logits32 = nullptr, *state = nullptr;
+  void *hx = nullptr, *pbuf = nullptr, *ubuf = nullptr, *mixbuf = nullptr, *obuf1 = nullptr, *obuf2 = nullptr, *ffbuf = nullptr;
+  void *moe_hidden = nullptr, *moe_out = nullptr, *hsel = nullptr;
+  int32_t *moe_goff = nullptr, *moe_ptok = nullptr, *moe_pdest = nullptr, *moe_cexp = nullptr;
+  float *moe_pw = nullptr, *moe_cw = nullptr;
+  int64_t slot_stride = 0;                   // floats per state slot
+  float* layer_dump_host = nullptr;          // diagnostics: residual stream after every layer of the next steps
+  int64_t layer_dump_cap = 0;
   const kge::Ops* op = &kge::kOpsBf16;
   ncclComm_t comm = nullptr;
   // peer-memory exchange (tp_peer.cu): created with the engine when tp_size > 1; h, xn and the gathered logits live in
@@ -162,4 +194,10 @@ inline namespace KGE_ELT_NS { int attn_decode_splits(int B, int KV, int max_seq_
 // second time, replayed afterwards.
 int engine_decode_step(kge_engine* e, int B, int stride, int max_seq_len, const StepMeta& dm, bool any_random, double sum_seq);
 StepMeta carve_meta(uint8_t* base, int T, int B, int R, int max_blocks, int64_t* total);
+// engine_hybrid.cu: weights, arena, caches, state pool and scheduler of a layer-list model; its forward pass
+int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, std::string* err);
+int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const StepMeta& m, bool any_random);
+int mask_step_logits(kge_engine* e);                       // engine_fwd.cu: the step's min_tokens bans on e->logits
+void fill_uniform(void* p, int64_t n, uint64_t seed, float scale, bool f16, cudaStream_t st);   // engine.cu (16-bit storage)
+void fill_const(void* p, int64_t n, float v, bool f16, cudaStream_t st);
 }  // namespace kge

@@ -238,7 +238,11 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
   const int T = b->T, B = b->B, R = b->R;
   KGE_REQUIRE(T > 0 && B > 0, "kge_step: empty batch");
   KGE_REQUIRE(T <= e->cfg.max_num_batched_tokens, "kge_step: T=%d exceeds max_num_batched_tokens=%d", T, e->cfg.max_num_batched_tokens);
-  KGE_REQUIRE(B <= e->cfg.max_num_seqs && R <= e->cfg.max_num_seqs, "kge_step: B=%d / R=%d exceed max_num_seqs=%d", B, R, e->cfg.max_num_seqs);
+  const bool hybrid = e->spec.is_hybrid();
+  // a layer-list model may be asked for the logits of any row of the step (trace replay); sampling needs R <= max_num_seqs
+  const int Rcap = hybrid ? std::max(e->cfg.max_num_seqs, e->cfg.max_num_batched_tokens) : e->cfg.max_num_seqs;
+  KGE_REQUIRE(B <= e->cfg.max_num_seqs && R <= Rcap, "kge_step: B=%d / R=%d exceed max_num_seqs=%d", B, R, e->cfg.max_num_seqs);
+  const bool sampled = R > 0 && R <= e->cfg.max_num_seqs;
   KGE_REQUIRE(b->max_blocks > 0 && b->max_blocks <= e->max_blocks_per_seq, "kge_step: max_blocks=%d out of range", b->max_blocks);
   KGE_CUDA_OK(cudaSetDevice(e->cfg.device));
   // pure decode step with every row sampled: block-table rows at a bucketed stride so the captured
@@ -263,6 +267,11 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
   }
   memcpy(hm.slots, b->slot_mapping, (size_t)T * 8);
   if (R > 0) memcpy(hm.rows, b->logits_rows, (size_t)R * 4);
+  for (int i = 0; i < B; ++i) {
+    hm.sslot[i] = b->state_slots ? b->state_slots[i] : i;
+    for (int t = b->query_start_loc[i]; t < b->query_start_loc[i + 1] && t < T; ++t) hm.treq[t] = i;
+    if (hybrid) KGE_REQUIRE(hm.sslot[i] >= 0 && hm.sslot[i] < e->cfg.max_num_seqs, "kge_step: request %d has state slot %d of %d", i, hm.sslot[i], e->cfg.max_num_seqs);
+  }
   bool any_random = false;
   for (int i = 0; i < R; ++i) {
     hm.temp[i] = temp ? temp[i] : 0.f;
@@ -307,7 +316,9 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
   KGE_CUDA_OK(cudaMemcpyAsync(e->meta_dev, e->meta_host, (size_t)bytes, cudaMemcpyHostToDevice, e->stream));
   e->h2d_bytes += bytes;
   e->d2h_bytes += (int64_t)R * 4;
-  if (decode_only && max_q == 1) {
+  if (hybrid) {
+    if (int rc = hybrid_forward(e, T, B, R, stride, dm, any_random)) return rc;
+  } else if (decode_only && max_q == 1) {
     if (int rc = engine_decode_step(e, B, stride, max_seq, dm, any_random, sum_seq)) return rc;
   } else {
     if (int rc = engine_forward(e, T, B, R, stride, max_q, max_seq, dm, any_random, sum_seq, attn_flops)) return rc;
@@ -315,8 +326,8 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
   ++e->step_count;
   e->lp_last_n = -1;
   if (R > 0) {
-    KGE_CUDA_OK(cudaMemcpyAsync(e->out_host, e->d_out, (size_t)R * 4, cudaMemcpyDeviceToHost, e->stream));
-    if (lp_n >= 0) {
+    if (sampled) KGE_CUDA_OK(cudaMemcpyAsync(e->out_host, e->d_out, (size_t)R * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (lp_n >= 0 && sampled) {
       // raw log-probabilities of the sampled tokens (vllm:v1/sample/sampler.py:300-349), for the rows that asked
       if (int rc = e->op->logprobs(e->lp_vals, e->lp_ids, e->lp_rank, e->logits, e->d_out, R, e->spec.vocab, e->spec.vocab, lp_n, e->stream)) return rc;
       ++e->launches;
@@ -327,7 +338,10 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
       e->d2h_bytes += (int64_t)(2 * n + (size_t)R * 4);
       e->lp_last_n = lp_n;
     }
-    if (out_logits_host) {
+    if (out_logits_host && hybrid) {
+      // layer-list models keep the logits of the step in fp32
+      KGE_CUDA_OK(cudaMemcpyAsync(out_logits_host, e->logits32, (size_t)R * e->spec.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+    } else if (out_logits_host) {
       // debug/parity path: logits as fp32 through a scratch carved from the (idle) gate_up buffer
       float* tmp = reinterpret_cast<float*>(e->gu);
       const int64_t n = (int64_t)R * e->spec.vocab;
@@ -339,7 +353,17 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
   }
   KGE_CUDA_OK(cudaStreamSynchronize(e->stream));
   if (e->timing) collect_timing(e);
-  if (R > 0 && out_ids_host) memcpy(out_ids_host, e->out_host, (size_t)R * 4);
+  if (sampled && out_ids_host) memcpy(out_ids_host, e->out_host, (size_t)R * 4);
+  return 0;
+}
+
+// engine_hybrid.cu applies the min_tokens mask through this (the kernel lives here)
+int mask_step_logits(kge_engine* e) {
+  if (e->step_num_masks <= 0) return 0;
+  mask_logits_kernel<<<(e->step_num_masks + 127) / 128, 128, 0, e->stream>>>(e->logits, e->mask_pairs, e->step_num_masks, e->spec.vocab, e->spec.vocab, e->f16);
+  KGE_LAUNCH_OK();
+  ++e->launches;
+  pdl_break_next();
   return 0;
 }
 
@@ -436,10 +460,11 @@ extern "C" int kge_engine_step(kge_engine* e, kge_step_output* outs, int32_t cap
   e->lp_last.clear();
   int max_blocks = 1;
   for (auto& s : sc) max_blocks = std::max(max_blocks, (int)s.req->blocks.size());
-  std::vector<int32_t> btab((size_t)B * max_blocks, 0);
+  std::vector<int32_t> btab((size_t)B * max_blocks, 0), sslot((size_t)B, 0);
   e->rec_pending_src.clear();
   for (int i = 0; i < B; ++i) {
     Request* r = sc[i].req;
+    sslot[i] = r->state_slot >= 0 ? r->state_slot : i;
     const int n = sc[i].num_tokens, start = r->num_computed - n;
     for (int t = start; t < start + n; ++t) {
       if (e->recording) {
@@ -486,6 +511,7 @@ extern "C" int kge_engine_step(kge_engine* e, kge_step_output* outs, int32_t cap
   b.token_ids = ids.data(); b.positions = pos.data(); b.query_start_loc = qsl.data();
   b.seq_lens = seq_lens.data(); b.block_table = btab.data(); b.max_blocks = max_blocks;
   b.slot_mapping = slots.data(); b.logits_rows = rows.data(); b.R = (int)rows.size();
+  b.state_slots = sslot.data();
   e->step_num_masks = n_masks;
   if (n_masks > 0)
     KGE_CUDA_OK(cudaMemcpyAsync(e->mask_pairs, e->mask_pairs_host, (size_t)n_masks * 8, cudaMemcpyHostToDevice, e->stream));
@@ -506,6 +532,77 @@ extern "C" int kge_engine_step(kge_engine* e, kge_step_output* outs, int32_t cap
     outs[i].num_scheduled = res[i].num_scheduled;
   }
   return (int)res.size();
+}
+
+// ------------------------------------------------------------- trace replay (scripted steps, logits out)
+extern "C" int kge_trace_add(kge_engine* e, int64_t request_id, const int32_t* token_ids, int32_t n) {
+  KGE_REQUIRE(e && token_ids && n > 0, "kge_trace_add: bad arguments");
+  for (int i = 0; i < n; ++i)
+    KGE_REQUIRE(token_ids[i] >= 0 && token_ids[i] < e->spec.vocab, "kge_trace_add: token id %d out of vocabulary", token_ids[i]);
+  const char* why = nullptr;
+  if (e->sched->find(request_id)) {
+    if (!e->sched->extend_prompt(request_id, token_ids, n, &why)) { kge::set_error("kge_trace_add: %s", why ? why : "rejected"); return -1; }
+    return 0;
+  }
+  SamplingParams sp;
+  sp.max_tokens = 1; sp.temperature = 0.f; sp.ignore_eos = true;
+  if (!e->sched->add(request_id, token_ids, n, sp, &why)) { kge::set_error("kge_trace_add: %s", why ? why : "rejected"); return -1; }
+  return 0;
+}
+
+extern "C" int kge_trace_step(kge_engine* e, const int64_t* request_ids, const int32_t* num_tokens, int32_t n,
+                              const int32_t* want_start, const int32_t* want, float* out_logits_host) {
+  KGE_REQUIRE(e && request_ids && num_tokens && n > 0 && want_start, "kge_trace_step: bad arguments");
+  std::vector<std::pair<int64_t, int32_t>> plan;
+  for (int i = 0; i < n; ++i) plan.push_back({request_ids[i], num_tokens[i]});
+  const char* why = nullptr;
+  if (!e->sched->schedule_scripted(plan, &why)) { kge::set_error("kge_trace_step: %s", why ? why : "rejected"); return -1; }
+  const std::vector<Scheduled>& sc = e->sched->scheduled();
+  const int bs = e->cfg.block_size, B = (int)sc.size();
+  std::vector<int32_t> ids, pos, qsl(1, 0), seq_lens, rows, sslot;
+  std::vector<int64_t> slots;
+  int max_blocks = 1;
+  for (auto& s : sc) max_blocks = std::max(max_blocks, (int)s.req->blocks.size());
+  std::vector<int32_t> btab((size_t)B * max_blocks, 0);
+  for (int i = 0; i < B; ++i) {
+    Request* r = sc[i].req;
+    const int cnt = sc[i].num_tokens, start = r->num_computed - cnt, row0 = (int)ids.size();
+    for (int t = start; t < start + cnt; ++t) {
+      ids.push_back(r->token_at(t));
+      pos.push_back(t);
+      slots.push_back((int64_t)r->blocks[t / bs] * bs + t % bs);
+    }
+    qsl.push_back((int)ids.size());
+    seq_lens.push_back(start + cnt);
+    sslot.push_back(r->state_slot >= 0 ? r->state_slot : i);
+    std::copy(r->blocks.begin(), r->blocks.end(), btab.begin() + (size_t)i * max_blocks);
+    for (int k = want_start[i]; k < want_start[i + 1]; ++k) {
+      KGE_REQUIRE(want && want[k] >= 0 && want[k] < cnt, "kge_trace_step: wanted place %d of %d tokens", want ? want[k] : -1, cnt);
+      rows.push_back(row0 + want[k]);
+    }
+  }
+  KGE_REQUIRE(rows.empty() || out_logits_host, "kge_trace_step: logits are wanted but there is no buffer for them");
+  kge_step_batch b;
+  b.T = (int)ids.size(); b.B = B;
+  b.token_ids = ids.data(); b.positions = pos.data(); b.query_start_loc = qsl.data();
+  b.seq_lens = seq_lens.data(); b.block_table = btab.data(); b.max_blocks = max_blocks;
+  b.slot_mapping = slots.data(); b.logits_rows = rows.data(); b.R = (int)rows.size();
+  b.state_slots = sslot.data();
+  e->step_num_masks = 0;
+  e->lp_last.clear();
+  return run_step(e, &b, nullptr, nullptr, nullptr, nullptr, nullptr, rows.empty() ? nullptr : out_logits_host);
+}
+
+extern "C" int kge_trace_end(kge_engine* e, int64_t request_id) {
+  KGE_REQUIRE(e, "kge_trace_end: null engine");
+  return e->sched->abort(request_id) ? 0 : -1;
+}
+
+extern "C" int kge_engine_set_layer_dump(kge_engine* e, float* host_buffer, int64_t capacity_floats) {
+  KGE_REQUIRE(e && e->spec.is_hybrid(), "kge_engine_set_layer_dump: layer-list models only");
+  e->layer_dump_host = host_buffer;
+  e->layer_dump_cap = host_buffer ? capacity_floats : 0;
+  return 0;
 }
 
 extern "C" int kge_engine_run_to_completion(kge_engine* e, kge_step_output* events, int64_t cap, int64_t* n_events,

@@ -1,0 +1,413 @@
+// Layer-list ("hybrid") models in the engine: a config.json that lists its layers, each with a token mixer (gated
+// linear recurrence, or attention and a matrix memory side by side) and a feed-forward (dense or mixture of experts),
+// both reading ONE norm of an fp32 residual stream.  This file loads such a model (weights in the engine's storage
+// type, fused where one activation feeds several projections), sizes its arena, paged caches and recurrent-state pool,
+// and runs its step: the same flattened batch, block tables and slot mapping as every other model, plus a state slot
+// per request.  Nothing here depends on how a prompt was cut into steps: recurrences continue from the slot, attention
+// reads the paged cache, and every other operation is per row.
+#include <string.h>
+
+#include <algorithm>
+
+#include "engine.h"
+#include "hybrid_ops.h"
+
+using namespace kge;
+
+namespace kge {
+
+namespace {
+
+struct HB {
+  kge_engine* e;
+  const ModelDir* md;
+  int64_t dummy_seed;
+  uint64_t counter = 1;
+  std::string err;
+  bool dummy() const { return !md->has_weights(); }
+  int esz() const { return e->f32 ? 4 : 2; }
+
+  void* dalloc(int64_t elems, int bytes_per) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, (size_t)std::max<int64_t>(elems, 8) * bytes_per) != cudaSuccess) {
+      err = std::string("cudaMalloc failed: ") + cudaGetErrorString(cudaGetLastError());
+      return nullptr;
+    }
+    e->allocs.push_back(p);
+    return p;
+  }
+  void* upload(const std::vector<float>& v) {
+    void* p = dalloc((int64_t)v.size(), esz());
+    if (!p) return nullptr;
+    e->weight_bytes += (int64_t)v.size() * esz();
+    cudaError_t ce;
+    if (e->f32) ce = cudaMemcpy(p, v.data(), v.size() * 4, cudaMemcpyHostToDevice);
+    else {
+      std::vector<uint16_t> h(v.size());
+      for (size_t i = 0; i < v.size(); ++i) {            // round to nearest even (exact for bfloat16 checkpoints)
+        uint32_t u; memcpy(&u, &v[i], 4);
+        if ((u & 0x7fffffffu) > 0x7f800000u) h[i] = (uint16_t)((u >> 16) | 0x40);
+        else { u += 0x7fffu + ((u >> 16) & 1u); h[i] = (uint16_t)(u >> 16); }
+      }
+      ce = cudaMemcpy(p, h.data(), h.size() * 2, cudaMemcpyHostToDevice);
+    }
+    if (ce != cudaSuccess) { err = "cudaMemcpy of weights failed"; return nullptr; }
+    return p;
+  }
+  // tensors stacked along their first dimension; every one must have `inner` elements per leading index
+  bool stack(const std::vector<std::string>& names, const std::vector<int64_t>& lead, int64_t inner, std::vector<float>* out) {
+    out->clear();
+    for (size_t i = 0; i < names.size(); ++i) {
+      const HostTensor* t = md->find(names[i]);
+      if (!t) { err = "missing tensor " + names[i]; return false; }
+      if (t->numel() != lead[i] * inner || (inner > 1 && t->shape.size() >= 2 && t->shape.back() != inner && t->shape.size() == 2)) {
+        err = names[i] + ": checkpoint shape does not match config.json (expected " + std::to_string(lead[i]) + " x " + std::to_string(inner) + ")";
+        return false;
+      }
+      std::vector<float> v;
+      if (!md->read_f32(names[i], &v, &err)) return false;
+      out->insert(out->end(), v.begin(), v.end());
+    }
+    return true;
+  }
+  // a matrix [sum(lead), K] (rows stacked), or random / constant values for a model without a checkpoint
+  void* mat(const std::vector<std::string>& names, const std::vector<int64_t>& lead, int64_t inner, float dummy_scale, float dummy_const = 0.f) {
+    int64_t rows = 0;
+    for (auto l : lead) rows += l;
+    if (dummy()) {
+      if (e->f32) { err = "random weights are made in bfloat16 only"; return nullptr; }
+      void* p = dalloc(rows * inner, 2);
+      if (!p) return nullptr;
+      e->weight_bytes += rows * inner * 2;
+      if (dummy_scale > 0.f) fill_uniform(p, rows * inner, (uint64_t)dummy_seed * 0x100000001B3ull + (counter++) * 0x9E3779B9ull, dummy_scale, false, e->stream);
+      else fill_const(p, rows * inner, dummy_const, false, e->stream);
+      return p;
+    }
+    std::vector<float> v;
+    if (!stack(names, lead, inner, &v)) return nullptr;
+    return upload(v);
+  }
+};
+
+int64_t align_up64(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, std::string* err) {
+  const ModelSpec& s = e->spec;
+  HB b{e, &md, dummy_seed};
+  const int d = s.d;
+  auto fail = [&](const std::string& m) { *err = m; return -1; };
+  const float ws = 0.02f * 1.7320508f;
+#define HB_OK(p) do { if (!(p)) return fail(b.err); } while (0)
+  HB_OK(e->embed = (bf16*)b.mat({"embed"}, {s.vocab}, d, ws));
+  HB_OK(e->lm_head = (bf16*)b.mat({"head"}, {s.vocab}, d, ws));
+  HB_OK(e->final_w = (bf16*)b.mat({"final.norm"}, {d}, 1, 0.f, 0.f));
+  e->hyb.resize(s.L);
+  int64_t state_floats = 0;
+  int max_proj = 1, max_mix = 1, max_ff = 1, max_gate = 1, max_u = 1, max_top = 0, max_eff = 1, max_E = 1;
+  for (int i = 0; i < s.L; ++i) {
+    const HybridLayerSpec& h = s.hybrid[i];
+    HybridLayerW& L = e->hyb[i];
+    const std::string p = "l" + std::to_string(i) + ".", mx = p + "mix.", fp = p + "mlp.";
+    HB_OK(L.norm1 = b.mat({p + "norm1"}, {d}, 1, 0.f, 0.f));
+    L.state_off = state_floats;
+    if (h.mixer == HybridLayerSpec::RGLRU) {
+      const int w = h.width, bw = w / h.blocks;
+      L.yx.N = 2 * w; L.yx.K = d;
+      HB_OK(L.yx.w = b.mat({mx + "y", mx + "x"}, {w, w}, d, ws));
+      HB_OK(L.yx.b = b.mat({mx + "y.b", mx + "x.b"}, {w, w}, 1, 0.f, 0.f));
+      HB_OK(L.conv_w = b.mat({mx + "conv"}, {w}, h.conv, 0.3f));
+      HB_OK(L.conv_b = b.mat({mx + "conv.b"}, {w}, 1, 0.f, 0.f));
+      L.ra.N = bw; L.ra.K = bw; L.ri.N = bw; L.ri.K = bw;
+      HB_OK(L.ra.w = b.mat({mx + "ra"}, {(int64_t)h.blocks * bw}, bw, 0.1f));
+      HB_OK(L.ra.b = b.mat({mx + "ra.b"}, {w}, 1, 0.f, 0.f));
+      HB_OK(L.ri.w = b.mat({mx + "ri"}, {(int64_t)h.blocks * bw}, bw, 0.1f));
+      HB_OK(L.ri.b = b.mat({mx + "ri.b"}, {w}, 1, 0.f, 0.f));
+      HB_OK(L.lam = b.mat({mx + "lam"}, {w}, 1, 0.f, -1.0f));
+      L.o.N = d; L.o.K = w;
+      HB_OK(L.o.w = b.mat({mx + "o"}, {d}, w, ws));
+      state_floats += rglru_state_floats(w, h.conv);
+      max_proj = std::max(max_proj, 2 * w); max_mix = std::max(max_mix, w); max_gate = std::max(max_gate, 2 * w); max_u = std::max(max_u, w);
+    } else {
+      const int nq = h.heads * h.dim, nk = h.kv_heads * h.dim, nv = h.kv_heads * h.vdim, mq = h.m_heads * h.m_dim, mv = h.m_heads * h.m_vdim;
+      L.off_k = nq; L.off_v = nq + nk; L.off_mq = L.off_v + nv; L.off_mk = L.off_mq + mq; L.off_mv = L.off_mk + mq; L.off_mg = L.off_mv + mv;
+      L.proj.N = L.off_mg + mv; L.proj.K = d;
+      const std::string a = mx + "left.", r = mx + "right.";
+      HB_OK(L.proj.w = b.mat({a + "q", a + "k", a + "v", r + "q", r + "k", r + "v", r + "g"}, {nq, nk, nv, mq, mq, mv, mv}, d, ws));
+      L.gates.N = 2 * h.m_heads; L.gates.K = d;
+      HB_OK(L.gates.w = b.mat({r + "i", r + "f"}, {h.m_heads, h.m_heads}, d, ws));
+      HB_OK(L.gates.b = b.mat({r + "i.b", r + "f.b"}, {h.m_heads, h.m_heads}, 1, 0.f, 1.f));
+      HB_OK(L.m_norm = b.mat({r + "norm"}, {mv}, 1, 0.f, 1.f));
+      // one output projection over [attention | matrix memory]: rows of the two matrices side by side
+      const int ka = h.heads * h.vdim, ko = ka + mv;
+      L.o2.N = d; L.o2.K = ko;
+      if (b.dummy()) HB_OK(L.o2.w = b.mat({}, {d}, ko, ws));
+      else {
+        std::vector<float> lo, ro, cat((size_t)d * ko);
+        if (!b.stack({a + "o"}, {d}, ka, &lo) || !b.stack({r + "o"}, {d}, mv, &ro)) return fail(b.err);
+        for (int n = 0; n < d; ++n) {
+          memcpy(&cat[(size_t)n * ko], &lo[(size_t)n * ka], (size_t)ka * 4);
+          memcpy(&cat[(size_t)n * ko + ka], &ro[(size_t)n * mv], (size_t)mv * 4);
+        }
+        HB_OK(L.o2.w = b.upload(cat));
+      }
+      state_floats += mlstm_state_floats(h.m_heads, h.m_dim, h.m_vdim);
+      max_proj = std::max(max_proj, L.proj.N); max_mix = std::max(max_mix, ko); max_gate = std::max(max_gate, 2 * h.m_heads);
+    }
+    if (h.mlp == HybridLayerSpec::DENSE) {
+      L.up.N = h.ff; L.up.K = d; L.down.N = d; L.down.K = h.ff;
+      HB_OK(L.up.w = b.mat({fp + "up"}, {h.ff}, d, ws));
+      HB_OK(L.down.w = b.mat({fp + "down"}, {d}, h.ff, ws));
+      max_ff = std::max(max_ff, h.ff);
+    } else if (h.mlp == HybridLayerSpec::MOE) {
+      L.router.N = h.experts; L.router.K = d;
+      HB_OK(L.router.w = b.mat({fp + "router"}, {h.experts}, d, ws * 4));
+      std::vector<std::string> g, u, dn;
+      std::vector<int64_t> lf((size_t)h.experts, h.expert_ff), ld((size_t)h.experts, d);
+      for (int x = 0; x < h.experts; ++x) { const std::string ep = fp + "e" + std::to_string(x) + "."; g.push_back(ep + "gate"); u.push_back(ep + "up"); dn.push_back(ep + "down"); }
+      HB_OK(L.e_gate = b.mat(g, lf, d, ws));
+      HB_OK(L.e_up = b.mat(u, lf, d, ws));
+      HB_OK(L.e_down = b.mat(dn, ld, h.expert_ff, ws));
+      if (h.shared_ff > 0) {
+        L.s_gate.N = L.s_up.N = h.shared_ff; L.s_gate.K = L.s_up.K = d; L.s_down.N = d; L.s_down.K = h.shared_ff;
+        HB_OK(L.s_gate.w = b.mat({fp + "shared.gate"}, {h.shared_ff}, d, ws));
+        HB_OK(L.s_up.w = b.mat({fp + "shared.up"}, {h.shared_ff}, d, ws));
+        HB_OK(L.s_down.w = b.mat({fp + "shared.down"}, {d}, h.shared_ff, ws));
+        max_ff = std::max(max_ff, h.shared_ff);
+      }
+      max_top = std::max(max_top, h.top); max_eff = std::max(max_eff, h.expert_ff); max_E = std::max(max_E, h.experts);
+    }
+  }
+#undef HB_OK
+  e->slot_stride = std::max<int64_t>(state_floats, 1);
+
+  const int Tm = e->cfg.max_num_batched_tokens, Rm = e->cfg.max_num_seqs, es = b.esz();
+  e->ld_logits = (int)align_up64(s.vocab, 64);
+  e->vocab_shard = e->vocab_loc = s.vocab; e->vocab_col0 = 0;
+  auto aalloc = [&](int64_t elems, int esz) -> void* { return b.dalloc(elems, esz); };
+  e->res32 = (float*)aalloc((int64_t)Tm * d, 4);
+  e->hx = aalloc((int64_t)Tm * d, es);
+  e->pbuf = aalloc((int64_t)Tm * max_proj, es);
+  e->ubuf = aalloc((int64_t)Tm * max_u, es);
+  e->mixbuf = aalloc((int64_t)Tm * max_mix, es);
+  e->obuf1 = aalloc((int64_t)Tm * d, es);
+  e->obuf2 = aalloc((int64_t)Tm * d, es);
+  e->ffbuf = aalloc((int64_t)Tm * max_ff, es);
+  e->gates32 = (float*)aalloc((int64_t)Tm * max_gate, 4);
+  e->hsel = aalloc((int64_t)Rm * d, es);
+  // logits rows: the sampled rows of a step, or every row a trace asks for
+  e->logits32 = (float*)aalloc((int64_t)std::max(Rm, Tm) * s.vocab, 4);
+  e->logits = (bf16*)aalloc((int64_t)Rm * e->ld_logits, 2);
+  e->state = (float*)aalloc((int64_t)Rm * e->slot_stride, 4);
+  if (max_top > 0) {
+    const int64_t np = (int64_t)Tm * max_top;
+    e->moe_hidden = aalloc(np * max_eff, es);
+    e->moe_out = aalloc(np * d, es);
+    e->moe_goff = (int32_t*)aalloc(max_E + 1, 4);
+    e->moe_ptok = (int32_t*)aalloc(np, 4); e->moe_pdest = (int32_t*)aalloc(np, 4); e->moe_cexp = (int32_t*)aalloc(np, 4);
+    e->moe_pw = (float*)aalloc(np, 4); e->moe_cw = (float*)aalloc(np, 4);
+    if (!e->moe_hidden || !e->moe_out || !e->moe_goff || !e->moe_ptok || !e->moe_pdest || !e->moe_cexp || !e->moe_pw || !e->moe_cw) return fail(b.err);
+  }
+  e->d_out = (int32_t*)aalloc(Rm, 4);
+  e->lp_vals = (float*)aalloc((int64_t)Rm * 21, 4);
+  e->lp_ids = (int32_t*)aalloc((int64_t)Rm * 21, 4);
+  e->lp_rank = (int32_t*)aalloc(Rm, 4);
+  e->mask_pairs = (int32_t*)aalloc(2 * kge_engine::kMaxMaskPairs, 4);
+  e->max_blocks_per_seq = (e->cfg.max_model_len + e->cfg.block_size - 1) / e->cfg.block_size;
+  carve_meta(nullptr, Tm, Rm, std::max(Rm, Tm), e->max_blocks_per_seq, &e->meta_bytes);
+  e->meta_dev = (uint8_t*)aalloc(e->meta_bytes, 1);
+  if (!e->res32 || !e->hx || !e->pbuf || !e->ubuf || !e->mixbuf || !e->obuf1 || !e->obuf2 || !e->ffbuf || !e->gates32 || !e->hsel ||
+      !e->logits32 || !e->logits || !e->state || !e->d_out || !e->lp_vals || !e->lp_ids || !e->lp_rank || !e->mask_pairs || !e->meta_dev)
+    return fail("activation arena allocation failed: " + b.err);
+  if (cudaMallocHost((void**)&e->meta_host, e->meta_bytes) != cudaSuccess ||
+      cudaMallocHost((void**)&e->out_host, (size_t)Rm * 4) != cudaSuccess ||
+      cudaMallocHost((void**)&e->lp_vals_host, (size_t)Rm * 21 * 4) != cudaSuccess ||
+      cudaMallocHost((void**)&e->lp_ids_host, (size_t)Rm * 21 * 4) != cudaSuccess ||
+      cudaMallocHost((void**)&e->lp_rank_host, (size_t)Rm * 4) != cudaSuccess ||
+      cudaMallocHost((void**)&e->mask_pairs_host, (size_t)2 * kge_engine::kMaxMaskPairs * 4) != cudaSuccess)
+    return fail("pinned staging allocation failed");
+  cudaMemsetAsync(e->state, 0, (size_t)Rm * e->slot_stride * 4, e->stream);
+
+  // paged caches of the attention sides: K [blocks, G, block_size, dim], V [blocks, G, block_size, vdim] per layer
+  int64_t blk_bytes = 0;
+  for (auto& h : s.hybrid)
+    if (h.mixer == HybridLayerSpec::PARALLEL) blk_bytes += (int64_t)h.kv_heads * e->cfg.block_size * (h.dim + h.vdim) * es;
+  int nb = e->cfg.num_blocks;
+  if (nb <= 0) {
+    const int64_t cap = (int64_t)e->cfg.max_num_seqs * e->max_blocks_per_seq + 1;
+    if (blk_bytes == 0) nb = (int)cap;
+    else {
+      size_t free_b = 0, total_b = 0;
+      cudaMemGetInfo(&free_b, &total_b);
+      const int64_t budget = (int64_t)((double)total_b * e->cfg.gpu_memory_utilization) - (int64_t)(total_b - free_b);
+      nb = (int)std::min<int64_t>(std::max<int64_t>(0, budget / blk_bytes), cap);
+    }
+  }
+  if (nb < 2) return fail("no memory left for the KV cache");
+  // a request holds at most max_model_len - 1 computed tokens (the last sampled token is never fed back)
+  if ((int64_t)(nb - 1) * e->cfg.block_size < e->cfg.max_model_len - 1)
+    return fail("the model's max seq len (" + std::to_string(e->cfg.max_model_len) + ") is larger than the number of tokens the KV cache can hold (" +
+                std::to_string((int64_t)(nb - 1) * e->cfg.block_size) + "); raise num_blocks / gpu_memory_utilization or lower max_model_len");
+  e->num_blocks = nb;
+  e->kv_bytes = blk_bytes * nb;
+  for (int i = 0; i < s.L; ++i) {
+    const HybridLayerSpec& h = s.hybrid[i];
+    if (h.mixer != HybridLayerSpec::PARALLEL) continue;
+    const int64_t nk = (int64_t)nb * h.kv_heads * e->cfg.block_size * h.dim, nv = (int64_t)nb * h.kv_heads * e->cfg.block_size * h.vdim;
+    e->hyb[i].kc = aalloc(nk, es); e->hyb[i].vc = aalloc(nv, es);
+    if (!e->hyb[i].kc || !e->hyb[i].vc) return fail("KV pool allocation failed");
+    cudaMemsetAsync(e->hyb[i].kc, 0, (size_t)nk * es, e->stream);
+    cudaMemsetAsync(e->hyb[i].vc, 0, (size_t)nv * es, e->stream);
+  }
+  SchedConfig sc;
+  sc.max_num_seqs = e->cfg.max_num_seqs;
+  sc.max_num_batched_tokens = e->cfg.max_num_batched_tokens;
+  sc.max_model_len = e->cfg.max_model_len;
+  sc.block_size = e->cfg.block_size;
+  sc.num_blocks = nb;
+  sc.enable_chunked_prefill = e->cfg.enable_chunked_prefill != 0;
+  sc.eos_token_id = s.eos;
+  sc.num_state_slots = e->cfg.max_num_seqs;        // every running request owns a slot of the recurrent-state pool
+  e->sched.reset(new Scheduler(sc));
+  e->use_graphs = false;
+  if (cudaStreamSynchronize(e->stream) != cudaSuccess) return fail(std::string("device error during initialisation: ") + cudaGetErrorString(cudaGetLastError()));
+  return 0;
+}
+
+#define HFWD(call)            \
+  do {                        \
+    int _rc = (call);         \
+    if (_rc) return _rc;      \
+    ++e->launches;            \
+  } while (0)
+
+// y[T, N] = act(x[T, K] w^T + b) in the engine's storage type (fp32 output where asked)
+static int dense(kge_engine* e, void* y, int ldy, const void* x, int ldx, const HybMat& m, int T, int act, bool out_f32 = false) {
+  LinearArgs a;
+  a.x = x; a.ldx = ldx; a.w = m.w; a.bias = m.b; a.y = y; a.ldy = ldy; a.T = T; a.N = m.N; a.K = m.K; a.act = act;
+  a.elt = e->f32 ? KGE_ELT_F32 : KGE_ELT_BF16; a.out_f32 = out_f32 || e->f32;
+  return linear_any(a, e->stream);
+}
+
+int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const StepMeta& m, bool any_random) {
+  const ModelSpec& s = e->spec;
+  const int d = s.d, elt = e->f32 ? KGE_ELT_F32 : KGE_ELT_BF16, es = e->f32 ? 4 : 2, bs = e->cfg.block_size;
+  cudaStream_t st = e->stream;
+  auto at = [&](void* base, int64_t elems) -> void* { return (uint8_t*)base + elems * es; };
+  HFWD(embed_f32(e->res32, m.ids, e->embed, T, d, elt, st));
+  for (int i = 0; i < s.L; ++i) {
+    const HybridLayerSpec& h = s.hybrid[i];
+    const HybridLayerW& L = e->hyb[i];
+    HFWD(rmsnorm_f32in(e->hx, e->res32, nullptr, L.norm1, T, d, s.eps, 1.f, elt, st));
+    CombineArgs cb;
+    auto add_src = [&](const void* p, int ld, float scale) { cb.src[cb.n] = p; cb.ld[cb.n] = ld; cb.scale[cb.n] = scale; ++cb.n; };
+    auto flush = [&]() -> int { if (cb.n == 0) return 0; int rc = residual_combine(e->res32, cb, T, d, elt, st); cb = CombineArgs(); return rc; };
+    if (h.mixer == HybridLayerSpec::RGLRU) {
+      const int w = h.width, bw = w / h.blocks;
+      HFWD(dense(e, e->pbuf, 2 * w, e->hx, d, L.yx, T, ACT_NONE));
+      RglruArgs ra;
+      ra.yx = e->pbuf; ra.u = e->ubuf; ra.gates = e->gates32; ra.out = e->mixbuf;
+      ra.conv_w = L.conv_w; ra.conv_b = L.conv_b; ra.lam = L.lam;
+      ra.state = e->state + L.state_off; ra.slot_stride = e->slot_stride;
+      ra.slots = m.sslot; ra.qsl = m.qsl; ra.positions = m.pos; ra.token_req = m.treq;
+      ra.B = B; ra.T = T; ra.width = w; ra.taps = h.conv; ra.decay_c = 8.f; ra.elt = elt;
+      HFWD(rglru_conv(ra, st));
+      for (int gsel = 0; gsel < 2; ++gsel) {           // block-diagonal gate projections of u, kept in fp32
+        const HybMat& gm = gsel ? L.ri : L.ra;
+        LinearArgs a;
+        a.x = e->ubuf; a.ldx = w; a.w = gm.w; a.bias = gm.b; a.y = e->gates32 + (int64_t)gsel * w; a.ldy = 2 * w;
+        a.T = T; a.N = bw; a.K = bw; a.nz = h.blocks; a.x_zs = bw; a.w_zs = (int64_t)bw * bw; a.b_zs = bw; a.y_zs = bw;
+        a.elt = elt; a.out_f32 = true;
+        HFWD(linear_any(a, st));
+      }
+      HFWD(rglru_scan(ra, st));
+      HFWD(dense(e, e->obuf1, d, e->mixbuf, w, L.o, T, ACT_NONE));
+      add_src(e->obuf1, d, 1.f);
+    } else {
+      const int ka = h.heads * h.vdim, ko = L.o2.K, ldp = L.proj.N;
+      HFWD(dense(e, e->pbuf, ldp, e->hx, d, L.proj, T, ACT_NONE));
+      HFWD(dense(e, e->gates32, 2 * h.m_heads, e->hx, d, L.gates, T, ACT_NONE, true));
+      HFWD(kv_write_any(at(e->pbuf, L.off_k), ldp, at(e->pbuf, L.off_v), ldp, m.slots, L.kc, L.vc, T, h.kv_heads, h.dim, h.vdim, bs, elt, st));
+      AttnBiasArgs aa;
+      aa.q = e->pbuf; aa.ldq = ldp; aa.out = e->mixbuf; aa.ldo = ko; aa.k_cache = L.kc; aa.v_cache = L.vc;
+      aa.block_table = m.btab; aa.max_blocks = max_blocks; aa.seq_lens = m.seq_lens; aa.qsl = m.qsl; aa.positions = m.pos; aa.token_req = m.treq;
+      aa.B = B; aa.T = T; aa.H = h.heads; aa.G = h.kv_heads; aa.dim = h.dim; aa.vdim = h.vdim; aa.block_size = bs; aa.chunk = h.chunk;
+      aa.scale = h.scale; aa.bias_span = 8.f; aa.out_scale = h.left_scale; aa.elt = elt;
+      HFWD(attn_bias_chunk(aa, st));
+      MlstmArgs ma;
+      ma.q = at(e->pbuf, L.off_mq); ma.k = at(e->pbuf, L.off_mk); ma.v = at(e->pbuf, L.off_mv); ma.g = at(e->pbuf, L.off_mg); ma.ld = ldp;
+      ma.gates = e->gates32; ma.norm_w = L.m_norm; ma.out = at(e->mixbuf, ka); ma.ldo = ko;
+      ma.state = e->state + L.state_off; ma.slot_stride = e->slot_stride; ma.slots = m.sslot; ma.qsl = m.qsl; ma.positions = m.pos;
+      ma.B = B; ma.T = T; ma.H = h.m_heads; ma.dim = h.m_dim; ma.vdim = h.m_vdim;
+      ma.cap = h.gate_cap; ma.q_scale = 1.f / sqrtf((float)h.m_dim); ma.eps = s.eps; ma.den_eps = 1e-6f; ma.out_scale = h.right_scale; ma.elt = elt;
+      HFWD(mlstm_step(ma, st));
+      HFWD(dense(e, e->obuf1, d, e->mixbuf, ko, L.o2, T, ACT_NONE));
+      add_src(e->obuf1, d, 1.f);
+    }
+    if (h.mlp == HybridLayerSpec::DENSE) {
+      HFWD(dense(e, e->ffbuf, h.ff, e->hx, d, L.up, T, ACT_GELU_ERF));
+      HFWD(dense(e, e->obuf2, d, e->ffbuf, h.ff, L.down, T, ACT_NONE));
+      add_src(e->obuf2, d, 1.f);
+    } else if (h.mlp == HybridLayerSpec::MOE) {
+      MoeRouteArgs ra;
+      ra.h = e->hx; ra.ldh = d; ra.w_router = L.router.w; ra.T = T; ra.d = d; ra.E = h.experts; ra.top = h.top; ra.score_fn = 0; ra.renorm = false;
+      ra.group_off = e->moe_goff; ra.perm_token = e->moe_ptok; ra.perm_weight = e->moe_pw; ra.perm_dest = e->moe_pdest;
+      ra.choice_expert = e->moe_cexp; ra.choice_weight = e->moe_cw; ra.elt = elt;
+      HFWD(moe_route(ra, st));
+      ++e->launches;
+      const int np = T * h.top;
+      LinearArgs g;      // experts' gated front half on the gathered, weighted rows
+      g.x = e->hx; g.ldx = d; g.w = L.e_gate; g.w2 = L.e_up; g.y = e->moe_hidden; g.ldy = h.expert_ff; g.T = np; g.N = h.expert_ff; g.K = d;
+      g.nz = h.experts; g.w_zs = (int64_t)h.expert_ff * d; g.group_off = e->moe_goff; g.max_rows = np; g.xrows = e->moe_ptok; g.row_scale = e->moe_pw;
+      g.elt = elt; g.out_f32 = e->f32;
+      HFWD(linear_any(g, st));
+      LinearArgs dn;     // experts' down projection, scattered to row (token * top + choice)
+      dn.x = e->moe_hidden; dn.ldx = h.expert_ff; dn.w = L.e_down; dn.y = e->moe_out; dn.ldy = d; dn.T = np; dn.N = d; dn.K = h.expert_ff;
+      dn.nz = h.experts; dn.w_zs = (int64_t)d * h.expert_ff; dn.group_off = e->moe_goff; dn.max_rows = np; dn.yrows = e->moe_pdest;
+      dn.elt = elt; dn.out_f32 = e->f32;
+      HFWD(linear_any(dn, st));
+      if (h.shared_ff > 0) {
+        LinearArgs sg;
+        sg.x = e->hx; sg.ldx = d; sg.w = L.s_gate.w; sg.w2 = L.s_up.w; sg.y = e->ffbuf; sg.ldy = h.shared_ff; sg.T = T; sg.N = h.shared_ff; sg.K = d;
+        sg.elt = elt; sg.out_f32 = e->f32;
+        HFWD(linear_any(sg, st));
+        HFWD(dense(e, e->obuf2, d, e->ffbuf, h.shared_ff, L.s_down, T, ACT_NONE));
+      }
+      // sum in a fixed order: mixer, the token's experts by choice, the shared expert
+      for (int k = 0; k < h.top; ++k) {
+        if (cb.n == 4) HFWD(flush());
+        add_src(at(e->moe_out, (int64_t)k * d), h.top * d, 1.f);
+      }
+      if (h.shared_ff > 0) { if (cb.n == 4) HFWD(flush()); add_src(e->obuf2, d, 1.f); }
+    }
+    HFWD(flush());
+    if (e->layer_dump_host && (int64_t)(i + 1) * T * d <= e->layer_dump_cap) {
+      KGE_CUDA_OK(cudaMemcpyAsync(e->layer_dump_host + (int64_t)i * T * d, e->res32, (size_t)T * d * 4, cudaMemcpyDeviceToHost, st));
+      KGE_CUDA_OK(cudaStreamSynchronize(st));
+    }
+  }
+  if (R > 0) {
+    KGE_REQUIRE(R <= std::max(e->cfg.max_num_seqs, e->cfg.max_num_batched_tokens), "hybrid_forward: %d logits rows", R);
+    // norm and head for the asked rows only, in pieces of max_num_seqs rows (the size of the gathered-row buffer)
+    const int Rm = e->cfg.max_num_seqs;
+    for (int r0 = 0; r0 < R; r0 += Rm) {
+      const int n = std::min(Rm, R - r0);
+      HFWD(rmsnorm_f32in(e->hsel, e->res32, m.rows + r0, e->final_w, n, d, s.eps, 1.f, elt, st));
+      LinearArgs a;
+      a.x = e->hsel; a.ldx = d; a.w = e->lm_head; a.y = e->logits32 + (int64_t)r0 * s.vocab; a.ldy = s.vocab; a.T = n; a.N = s.vocab; a.K = d;
+      a.alpha = s.logit_scale; a.elt = elt; a.out_f32 = true;
+      HFWD(linear_any(a, st));
+    }
+    if (R <= Rm) {
+      // the samplers read 16-bit logits
+      HFWD(logits_to_elt16(e->logits, e->logits32, R, s.vocab, s.vocab, false, st));
+      if (int rc = mask_step_logits(e)) return rc;
+      if (any_random) HFWD(kge_sample(e->d_out, e->logits, R, s.vocab, s.vocab, m.temp, m.top_k, m.top_p, nullptr, m.seeds, 0, nullptr, 0, st));
+      else HFWD(kge_argmax(e->d_out, e->logits, R, s.vocab, s.vocab, st));
+    }
+  }
+  return 0;
+}
+
+}  // namespace kge

@@ -1,0 +1,123 @@
+// Launchers of the kernels that layer-list ("hybrid") models add to the library: a shape-agnostic linear layer with
+// grouped / gathered rows, fp32-residual norms, biased chunk-masked paged attention, the gated linear recurrence
+// (RG-LRU), the matrix memory (mLSTM) and the mixture-of-experts router.  Every mechanism takes its sizes and constants
+// as arguments.  `elt` names the storage type of activations and weights: KGE_ELT_BF16 or KGE_ELT_F32; what the
+// mechanisms compute in 32 bits (softmax, norms, routers, residual sums, recurrent state and everything that enters a
+// recurrence besides projections and short convolutions) is 32-bit in both.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace kge {
+
+enum { KGE_ELT_BF16 = 0, KGE_ELT_F32 = 1 };
+enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SIGMOID = 4 };
+
+inline size_t elt_size(int elt) { return elt == KGE_ELT_F32 ? 4 : 2; }
+
+// y[yr(r), n] (+)= alpha * act(scale_r * sum_k x[xr(r), k] * w[n, k] + bias[n])        (w2 == null)
+// y[yr(r), n] (+)= alpha * silu(scale_r * x.w[n]) * (scale_r * x.w2[n])                  (w2 != null: gated pair)
+// Rows r run over [0, T), or - with group_off - over [group_off[z], group_off[z+1]) for each z < nz, where slice z
+// reads x at column offset z * x_zs, weights at w + z * w_zs (elements), bias at z * b_zs and writes y at column offset
+// z * y_zs.  xrows / yrows (null = identity) gather the input row and scatter the output row; row_scale (null = 1) is
+// indexed by r.  Sums run over k in ascending order in fp32, whatever else is in the launch.
+struct LinearArgs {
+  const void* x = nullptr; int ldx = 0;
+  const void* w = nullptr; const void* w2 = nullptr; const void* bias = nullptr;
+  void* y = nullptr; int ldy = 0;
+  int T = 0, N = 0, K = 0;
+  int nz = 1; int64_t x_zs = 0, w_zs = 0, b_zs = 0, y_zs = 0;
+  const int32_t* group_off = nullptr;     // device [nz + 1]
+  int max_rows = 0;                        // with group_off: an upper bound of any group's row count (0 = T)
+  const int32_t* xrows = nullptr; const int32_t* yrows = nullptr;
+  const float* row_scale = nullptr;
+  int act = ACT_NONE; float alpha = 1.f; bool accumulate = false;
+  int elt = KGE_ELT_BF16; bool out_f32 = false;
+};
+int linear_any(const LinearArgs& a, cudaStream_t st);
+
+// res[t, :] = float(table[ids[t], :])
+int embed_f32(float* res, const int32_t* ids, const void* table, int T, int d, int elt, cudaStream_t st);
+// y[r, :] = x[rows ? rows[r] : r, :] / sqrt(mean(x^2) + eps) * (offset + w), x fp32, y in elt
+int rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, int elt, cudaStream_t st);
+// res[t, :] += sum_i scale[i] * src[i][t, :]   (up to 4 sources in elt, each [T, d] with its own leading dimension)
+struct CombineArgs { const void* src[4] = {nullptr, nullptr, nullptr, nullptr}; int ld[4] = {0, 0, 0, 0}; float scale[4] = {0, 0, 0, 0}; int n = 0; };
+int residual_combine(float* res, const CombineArgs& a, int T, int d, int elt, cudaStream_t st);
+// fp32 [R, V] -> 16-bit logits for the samplers (ld_out >= V)
+int logits_to_elt16(void* out, const float* in, int R, int V, int ld_out, bool f16, cudaStream_t st);
+
+// Paged attention with a per-head linear distance bias and an optional chunk mask.
+//   score(i, j) = scale * q_i . k_j - slope_h * (i - j),  slope_h = 2^(-bias_span * (h + 1) / H)   (bias_span = 0: no bias)
+//   j visible to i iff j <= i and (chunk == 0 or floor(i / chunk) == floor(j / chunk)), positions counted from the
+//   start of the sequence.  Softmax in fp32.  q rows are read from a packed projection buffer (row stride ldq elements,
+//   head h at column h * dim); K cache [num_blocks, G, block_size, dim], V cache [num_blocks, G, block_size, vdim].
+//   out [T, H * vdim] (row stride ldo), multiplied by out_scale.
+struct AttnBiasArgs {
+  const void* q = nullptr; int ldq = 0; void* out = nullptr; int ldo = 0;
+  const void* k_cache = nullptr; const void* v_cache = nullptr;
+  const int32_t* block_table = nullptr; int max_blocks = 0;
+  const int32_t* seq_lens = nullptr; const int32_t* qsl = nullptr; const int32_t* positions = nullptr;
+  const int32_t* token_req = nullptr;      // [T] request index of every token row
+  int B = 0, T = 0, H = 0, G = 0, dim = 0, vdim = 0, block_size = 0, chunk = 0;
+  float scale = 1.f, bias_span = 0.f, out_scale = 1.f;
+  int elt = KGE_ELT_BF16;
+};
+int attn_bias_chunk(const AttnBiasArgs& a, cudaStream_t st);
+// k / v rows of a packed projection buffer -> paged caches (slot = block * block_size + offset, < 0 skips)
+int kv_write_any(const void* k, int ldk, const void* v, int ldv, const int64_t* slots, void* k_cache, void* v_cache, int T, int G,
+                 int dim, int vdim, int block_size, int elt, cudaStream_t st);
+
+// Gated linear recurrence (RG-LRU).  yx [T, 2 * width]: the y branch's pre-activation, then the x branch (biases in).
+//   u = causal per-channel conv of x (taps weights per channel, last tap on the current token; inputs before position 0
+//       are zero; inputs before this step's first token come from the slot's conv tail)
+//   r = sigmoid(gate_r), i = sigmoid(gate_i): pre-activations of block-diagonal projections of u, given in fp32
+//   a = exp(-decay_c * r * softplus(lam));  S <- a S + sqrt(1 - a^2) * i * u;  out = S * gelu_tanh(y)
+// State per slot: S [width] and the last taps - 1 inputs of the conv, all fp32; a request whose first row is position 0
+// starts from zero.  rglru_conv writes u (elt); rglru_scan runs the recurrence and writes out (elt) and the state.
+struct RglruArgs {
+  const void* yx = nullptr; void* u = nullptr; const float* gates = nullptr;   // gates [T, 2 * width]: r then i
+  void* out = nullptr;
+  const void* conv_w = nullptr; const void* conv_b = nullptr; const void* lam = nullptr;
+  float* state = nullptr; int64_t slot_stride = 0;     // floats between slots; this layer's state starts at `state`
+  const int32_t* slots = nullptr; const int32_t* qsl = nullptr; const int32_t* positions = nullptr; const int32_t* token_req = nullptr;
+  int B = 0, T = 0, width = 0, taps = 1;
+  float decay_c = 8.f;
+  int elt = KGE_ELT_BF16;
+};
+int rglru_conv(const RglruArgs& a, cudaStream_t st);
+int rglru_scan(const RglruArgs& a, cudaStream_t st);
+inline int64_t rglru_state_floats(int width, int taps) { return (int64_t)width * taps; }   // S + (taps - 1) conv inputs
+
+// Matrix memory (mLSTM) with a running maximum m that starts at 0.
+//   i~ = cap * tanh(i_pre / cap), f~ = logsigmoid(cap * tanh(f_pre / cap))   (gate pre-activations in fp32, [T, 2 * H]: i then f)
+//   m' = max(f~ + m, i~);  S <- exp(f~ + m - m') S + exp(i~ - m') k v^T;  n likewise with k;  q scaled by q_scale
+//   o = S^T q / (max(|n . q|, exp(-m')) + den_eps), divided by its root mean square over vdim (eps), times norm_w,
+//   times sigmoid(gate) -> out [T, H * vdim], multiplied by out_scale.
+// State per slot and head: S [dim, vdim], n [dim], m, all fp32.
+struct MlstmArgs {
+  const void* q = nullptr; const void* k = nullptr; const void* v = nullptr; const void* g = nullptr; int ld = 0;   // one packed buffer
+  const float* gates = nullptr;
+  const void* norm_w = nullptr; void* out = nullptr; int ldo = 0;
+  float* state = nullptr; int64_t slot_stride = 0;
+  const int32_t* slots = nullptr; const int32_t* qsl = nullptr; const int32_t* positions = nullptr;
+  int B = 0, T = 0, H = 0, dim = 0, vdim = 0;
+  float cap = 1.f, q_scale = 1.f, eps = 1e-5f, den_eps = 1e-6f, out_scale = 1.f;
+  int elt = KGE_ELT_BF16;
+};
+int mlstm_step(const MlstmArgs& a, cudaStream_t st);
+inline int64_t mlstm_state_floats(int H, int dim, int vdim) { return (int64_t)H * ((int64_t)dim * vdim + dim + 1); }
+
+// Mixture-of-experts routing: logits z = W_router h in fp32, scores sigmoid(z) (score_fn 0) or softmax(z) (1), the `top`
+// largest chosen (ties to the lower index), weights = scores, renormalised to sum 1 if renorm.  Produces for every
+// expert the list of (token, choice) pairs routed to it: group_off [E + 1], perm_token [T * top] (the token row of
+// every permuted row), perm_weight [T * top], perm_dest [T * top] (row t * top + choice of the output buffer).
+struct MoeRouteArgs {
+  const void* h = nullptr; int ldh = 0; const void* w_router = nullptr;
+  int T = 0, d = 0, E = 0, top = 1, score_fn = 0; bool renorm = false;
+  int32_t* group_off = nullptr; int32_t* perm_token = nullptr; float* perm_weight = nullptr; int32_t* perm_dest = nullptr;
+  int32_t* choice_expert = nullptr; float* choice_weight = nullptr;     // scratch [T * top] each
+  int elt = KGE_ELT_BF16;
+};
+int moe_route(const MoeRouteArgs& a, cudaStream_t st);
+
+}  // namespace kge

@@ -1,0 +1,192 @@
+// Shape-agnostic linear layer for layer-list models: any T / N / K and alignment, bfloat16 or float32 storage, fp32
+// accumulation in ascending k (so a row's result does not depend on what else is in the launch), optional row gather /
+// scatter, per-row input scale, grouped rows (one weight slice per group: mixture-of-experts) or strided slices
+// (block-diagonal projections), gated pairs (silu(x.w) * (x.w2)) and fp32 output or accumulation.  Tiles of 64 x 64
+// outputs, 256 threads with 4 x 4 outputs each, operands staged in shared memory as fp32.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "elt_access.cuh"
+#include "hybrid_ops.h"
+
+namespace kge {
+
+__device__ __forceinline__ float act_apply(int act, float v) {
+  switch (act) {
+    case ACT_GELU_ERF: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+    case ACT_GELU_TANH: return 0.5f * v * (1.f + tanhf(0.79788456080286536f * (v + 0.044715f * v * v * v)));
+    case ACT_SILU: return v / (1.f + expf(-v));
+    case ACT_SIGMOID: return 1.f / (1.f + expf(-v));
+    default: return v;
+  }
+}
+
+constexpr int LBM = 64, LBN = 64, LBK = 16;
+
+template <typename E, typename O, bool DUAL>
+__global__ void __launch_bounds__(256) linear_any_kernel(LinearArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int z = blockIdx.z;
+  int r0 = 0, r1 = a.T;
+  if (a.group_off) { r0 = a.group_off[z]; r1 = a.group_off[z + 1]; }
+  const int m0 = r0 + blockIdx.y * LBM;
+  if (m0 >= r1) return;
+  const int n0 = blockIdx.x * LBN;
+  const E* x = (const E*)a.x + z * a.x_zs;
+  const E* w = (const E*)a.w + z * a.w_zs;
+  const E* w2 = DUAL ? (const E*)a.w2 + z * a.w_zs : nullptr;
+  const E* bias = a.bias ? (const E*)a.bias + z * a.b_zs : nullptr;
+  O* y = (O*)a.y + z * a.y_zs;
+  __shared__ float xs[LBK][LBM + 1], ws[LBK][LBN + 1], ws2[DUAL ? LBK : 1][LBN + 1];
+  __shared__ int xrow[LBM];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  if (tid < LBM) {
+    const int r = m0 + tid;
+    xrow[tid] = r < r1 ? (a.xrows ? a.xrows[r] : r) : -1;
+  }
+  __syncthreads();
+  float acc[4][4] = {}, acc2[DUAL ? 4 : 1][4] = {};
+  for (int k0 = 0; k0 < a.K; k0 += LBK) {
+    for (int i = tid; i < LBM * LBK; i += 256) {
+      const int r = i / LBK, k = i % LBK;
+      const int xr = xrow[r];
+      xs[k][r] = (xr >= 0 && k0 + k < a.K) ? ldf(x + (int64_t)xr * a.ldx + k0 + k) : 0.f;
+      const int n = n0 + r;
+      const bool ok = n < a.N && k0 + k < a.K;
+      ws[k][r] = ok ? ldf(w + (int64_t)n * a.K + k0 + k) : 0.f;
+      if (DUAL) ws2[k][r] = ok ? ldf(w2 + (int64_t)n * a.K + k0 + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < LBK; ++k) {
+      float xv[4], wv[4], wv2[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { xv[i] = xs[k][ty * 4 + i]; wv[i] = ws[k][tx * 4 + i]; if (DUAL) wv2[i] = ws2[k][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+          if (DUAL) acc2[i][j] = fmaf(xv[i], wv2[j], acc2[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = m0 + ty * 4 + i;
+    if (r >= r1) continue;
+    const float s = a.row_scale ? a.row_scale[r] : 1.f;
+    const int yr = a.yrows ? a.yrows[r] : r;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= a.N) continue;
+      float v;
+      if (DUAL) v = act_apply(ACT_SILU, s * acc[i][j]) * (s * acc2[i][j]);
+      else v = act_apply(a.act, s * acc[i][j] + (bias ? ldf(bias + n) : 0.f));
+      v *= a.alpha;
+      O* dst = y + (int64_t)yr * a.ldy + n;
+      if (a.accumulate) v += ldf(dst);
+      stf(dst, v);
+    }
+  }
+}
+
+int linear_any(const LinearArgs& a, cudaStream_t st) {
+  KGE_REQUIRE(a.x && a.w && a.y && a.N > 0 && a.K > 0 && a.nz > 0, "linear_any: bad arguments");
+  if (a.T <= 0) return 0;
+  const int rows = a.group_off ? (a.max_rows > 0 ? a.max_rows : a.T) : a.T;
+  dim3 grid((a.N + LBN - 1) / LBN, (rows + LBM - 1) / LBM, a.nz), block(256);
+  KGE_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "linear_any: too many row tiles (%u) or slices (%u)", grid.y, grid.z);
+  cudaError_t ce;
+  const bool f32 = a.elt == KGE_ELT_F32;
+  KGE_REQUIRE(!f32 || a.out_f32, "linear_any: float32 storage writes float32");
+  if (f32) ce = a.w2 ? launch_pdl(linear_any_kernel<float, float, true>, grid, block, 0, st, a) : launch_pdl(linear_any_kernel<float, float, false>, grid, block, 0, st, a);
+  else if (a.out_f32) ce = a.w2 ? launch_pdl(linear_any_kernel<__nv_bfloat16, float, true>, grid, block, 0, st, a) : launch_pdl(linear_any_kernel<__nv_bfloat16, float, false>, grid, block, 0, st, a);
+  else ce = a.w2 ? launch_pdl(linear_any_kernel<__nv_bfloat16, __nv_bfloat16, true>, grid, block, 0, st, a) : launch_pdl(linear_any_kernel<__nv_bfloat16, __nv_bfloat16, false>, grid, block, 0, st, a);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------ small row kernels
+template <typename E>
+__global__ void embed_f32_kernel(float* res, const int32_t* ids, const E* table, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const E* src = table + (int64_t)ids[t] * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) res[(int64_t)t * d + c] = ldf(src + c);
+}
+int embed_f32(float* res, const int32_t* ids, const void* table, int T, int d, int elt, cudaStream_t st) {
+  if (T <= 0) return 0;
+  cudaError_t ce = elt == KGE_ELT_F32 ? launch_pdl(embed_f32_kernel<float>, dim3(T), dim3(128), 0, st, res, ids, (const float*)table, d)
+                                      : launch_pdl(embed_f32_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, st, res, ids, (const __nv_bfloat16*)table, d);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+template <typename E>
+__global__ void rmsnorm_f32in_kernel(E* y, const float* x, const int32_t* rows, const E* w, int d, float eps, float offset) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const float* src = x + (int64_t)(rows ? rows[r] : r) * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) { const float v = src[c]; ss = fmaf(v, v, ss); }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)d + eps);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) stf(y + (int64_t)r * d + c, src[c] * inv * (offset + ldf(w + c)));
+}
+int rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, int elt, cudaStream_t st) {
+  if (R <= 0) return 0;
+  cudaError_t ce = elt == KGE_ELT_F32
+      ? launch_pdl(rmsnorm_f32in_kernel<float>, dim3(R), dim3(256), 0, st, (float*)y, x, rows, (const float*)w, d, eps, offset)
+      : launch_pdl(rmsnorm_f32in_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, st, (__nv_bfloat16*)y, x, rows, (const __nv_bfloat16*)w, d, eps, offset);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+template <typename E>
+__global__ void residual_combine_kernel(float* res, CombineArgs a, int64_t n, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / d; const int c = (int)(i % d);
+    float s = 0.f;
+    for (int k = 0; k < a.n; ++k) s = fmaf(a.scale[k], ldf((const E*)a.src[k] + t * a.ld[k] + c), s);
+    res[i] += s;
+  }
+}
+int residual_combine(float* res, const CombineArgs& a, int T, int d, int elt, cudaStream_t st) {
+  if (T <= 0 || a.n <= 0) return 0;
+  const int64_t n = (int64_t)T * d;
+  const int grid = (int)std::min<int64_t>((n + 255) / 256, 148 * 8);
+  cudaError_t ce = elt == KGE_ELT_F32 ? launch_pdl(residual_combine_kernel<float>, dim3(grid), dim3(256), 0, st, res, a, n, d)
+                                      : launch_pdl(residual_combine_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, res, a, n, d);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+__global__ void logits_to_elt16_kernel(uint16_t* out, const float* in, int R, int V, int ld, bool f16) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t n = (int64_t)R * V;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / V; const int c = (int)(i % V);
+    out[r * ld + c] = f16 ? __half_as_ushort(__float2half_rn(in[i])) : __bfloat16_as_ushort(__float2bfloat16_rn(in[i]));
+  }
+}
+int logits_to_elt16(void* out, const float* in, int R, int V, int ld_out, bool f16, cudaStream_t st) {
+  if (R <= 0) return 0;
+  const int grid = (int)std::min<int64_t>(((int64_t)R * V + 255) / 256, 148 * 8);
+  KGE_CUDA_OK(launch_pdl(logits_to_elt16_kernel, dim3(grid), dim3(256), 0, st, (uint16_t*)out, in, R, V, ld_out, f16));
+  return 0;
+}
+
+}  // namespace kge

@@ -30,7 +30,64 @@ static bool read_file(const std::string& path, std::string* out) {
   return true;
 }
 
+// Layer-list models: config.json carries "architecture" and a "layers" array instead of HF's flat sizes.
+static bool parse_hybrid(const Json& j, ModelSpec* s, std::string* err) {
+  s->model_type = "safupel";
+  s->vocab = (int)j.int_or("vocab", 0);
+  s->d = (int)j.int_or("width", 0);
+  s->logit_scale = (float)j.num_or("logit_scale", 1.0);
+  if (const Json* n = j.get("norm")) s->eps = (float)n->num_or("eps", 1e-5);
+  s->max_pos = 1 << 20;                 // positions enter through computed biases and masks only: no table bounds them
+  s->torch_dtype = "bfloat16";
+  s->bos = (int)j.int_or("bos_token_id", -1);
+  s->eos = (int)j.int_or("eos_token_id", -1);
+  const Json* ls = j.get("layers");
+  if (!ls || !ls->is_arr() || ls->arr.empty()) { *err = "config.json: 'layers' must be a non-empty array"; return false; }
+  for (const Json& l : ls->arr) {
+    HybridLayerSpec h;
+    const std::string type = l.str_or("type", "");
+    const Json* m = l.get("mixer");
+    if (!m || !m->is_obj()) { *err = "config.json: a layer has no 'mixer'"; return false; }
+    if (type == "rglru") {
+      h.mixer = HybridLayerSpec::RGLRU;
+      h.width = (int)m->int_or("width", 0); h.blocks = (int)m->int_or("blocks", 1); h.conv = (int)m->int_or("conv", 1);
+      if (h.width <= 0 || h.blocks <= 0 || h.width % h.blocks || h.conv < 1 || h.conv > 16) { *err = "config.json: bad rglru sizes"; return false; }
+    } else if (type == "parallel") {
+      h.mixer = HybridLayerSpec::PARALLEL;
+      const Json *a = m->get("left"), *r = m->get("right");
+      if (!a || !r) { *err = "config.json: a parallel mixer needs 'left' and 'right'"; return false; }
+      h.heads = (int)a->int_or("heads", 0); h.kv_heads = (int)a->int_or("kv_heads", h.heads);
+      h.dim = (int)a->int_or("dim", 0); h.vdim = (int)a->int_or("vdim", h.dim);
+      h.scale = (float)a->num_or("scale", 1.0);
+      if (const Json* mk = a->get("mask")) h.chunk = (int)mk->int_or("size", 0);
+      h.m_heads = (int)r->int_or("heads", 0); h.m_dim = (int)r->int_or("dim", 0); h.m_vdim = (int)r->int_or("vdim", h.m_dim);
+      h.gate_cap = (float)r->num_or("gate_cap", 0.0);
+      h.left_scale = (float)m->num_or("left_scale", 1.0); h.right_scale = (float)m->num_or("right_scale", 1.0);
+      if (h.heads <= 0 || h.kv_heads <= 0 || h.heads % h.kv_heads || h.dim <= 0 || h.vdim <= 0 || h.m_heads <= 0 || h.m_dim <= 0 ||
+          h.m_vdim <= 0 || h.gate_cap <= 0.f || h.chunk < 0) { *err = "config.json: bad parallel-mixer sizes"; return false; }
+    } else { *err = "config.json: unknown layer type '" + type + "' (rglru, parallel)"; return false; }
+    const Json* f = l.get("mlp");
+    if (f && f->is_obj()) {
+      const std::string kind = f->str_or("kind", "");
+      if (kind == "dense") { h.mlp = HybridLayerSpec::DENSE; h.ff = (int)f->int_or("ff", 0); if (h.ff <= 0) { *err = "config.json: dense mlp without ff"; return false; } }
+      else if (kind == "moe") {
+        h.mlp = HybridLayerSpec::MOE;
+        const Json *ex = f->get("expert"), *ro = f->get("router"), *sh = f->get("shared");
+        if (!ex || !ro) { *err = "config.json: moe mlp needs 'expert' and 'router'"; return false; }
+        h.expert_ff = (int)ex->int_or("ff", 0); h.experts = (int)ro->int_or("experts", 0); h.top = (int)ro->int_or("top", 1);
+        if (sh && sh->is_obj()) h.shared_ff = (int)sh->int_or("ff", 0);
+        if (h.expert_ff <= 0 || h.experts <= 0 || h.top <= 0 || h.top > h.experts) { *err = "config.json: bad moe sizes"; return false; }
+      } else { *err = "config.json: unknown mlp kind '" + kind + "'"; return false; }
+    }
+    s->hybrid.push_back(h);
+  }
+  s->L = (int)s->hybrid.size();
+  if (s->vocab <= 0 || s->d <= 0) { *err = "config.json misses a required size"; return false; }
+  return true;
+}
+
 static bool parse_config(const Json& j, ModelSpec* s, std::string* err) {
+  if (j.str_or("architecture", "") == "Safupel") return parse_hybrid(j, s, err);
   s->model_type = j.str_or("model_type", "");
   s->vocab = (int)j.int_or("vocab_size", 0);
   s->d = (int)j.int_or("hidden_size", 0);
@@ -138,9 +195,9 @@ bool ModelDir::open(const std::string& dir, std::string* err) {
       ht.dtype = t.str_or("dtype", "");
       for (auto& s : shp->arr) ht.shape.push_back((int64_t)s.num);
       const uint64_t b = (uint64_t)off->arr[0].num, e = (uint64_t)off->arr[1].num;
-      const int esz = ht.dtype == "F32" ? 4 : 2;
+      const int esz = (ht.dtype == "F32" || ht.dtype == "I32") ? 4 : 2;
       if (e > data_len || b > e || (e - b) != (uint64_t)ht.numel() * esz) { *err = path + ": bad offsets for " + kv.first; return false; }
-      if (ht.dtype != "BF16" && ht.dtype != "F16" && ht.dtype != "F32") { *err = kv.first + ": dtype " + ht.dtype + " unsupported"; return false; }
+      if (ht.dtype != "BF16" && ht.dtype != "F16" && ht.dtype != "F32" && ht.dtype != "I32") { *err = kv.first + ": dtype " + ht.dtype + " unsupported"; return false; }
       ht.data = data0 + b;
       tensors_[kv.first] = ht;
     }
@@ -188,6 +245,7 @@ bool ModelDir::read_16(const std::string& name, int64_t r0, int64_t r1, int64_t 
                        std::vector<uint16_t>* out, std::string* err) const {
   const HostTensor* t = find(name);
   if (!t) { *err = "missing tensor " + name; return false; }
+  if (t->dtype == "I32") { *err = name + ": an integer table cannot be read as a 16-bit float tensor"; return false; }
   int64_t rows, cols;
   if (t->shape.size() == 1) { rows = t->shape[0]; cols = 1; c0 = 0; c1 = 1; }
   else if (t->shape.size() == 2) { rows = t->shape[0]; cols = t->shape[1]; }
@@ -215,6 +273,20 @@ bool ModelDir::read_16(const std::string& name, int64_t r0, int64_t r1, int64_t 
       const float* s = (const float*)t->data + src;
       for (int64_t c = 0; c < nc; ++c) dst[c] = f16 ? f32_to_f16_bits(s[c]) : f32_bf16(s[c]);
     }
+  }
+  return true;
+}
+
+bool ModelDir::read_f32(const std::string& name, std::vector<float>* out, std::string* err) const {
+  const HostTensor* t = find(name);
+  if (!t) { *err = "missing tensor " + name; return false; }
+  const int64_t n = t->numel();
+  out->resize((size_t)n);
+  if (t->dtype == "F32") memcpy(out->data(), t->data, (size_t)n * 4);
+  else if (t->dtype == "I32") { const int32_t* s = (const int32_t*)t->data; for (int64_t i = 0; i < n; ++i) (*out)[i] = (float)s[i]; }
+  else {
+    const uint16_t* s = (const uint16_t*)t->data;
+    for (int64_t i = 0; i < n; ++i) (*out)[i] = t->dtype == "BF16" ? bf16_f32(s[i]) : f16_f32(s[i]);
   }
   return true;
 }

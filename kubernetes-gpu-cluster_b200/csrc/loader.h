@@ -9,8 +9,33 @@
 
 namespace kge {
 
+// One layer of a layer-list ("hybrid") model: which token mixer it has, that mixer's sizes and constants, and its
+// feed-forward.  Every number comes from config.json; the kernels take them as parameters.
+struct HybridLayerSpec {
+  enum Mixer { RGLRU = 0, PARALLEL = 1 };
+  enum Mlp { NONE = 0, DENSE = 1, MOE = 2 };
+  int mixer = RGLRU;
+  // gated linear recurrence (RG-LRU): two branches of `width`, gates block-diagonal in `blocks` parts, causal conv of `conv` taps
+  int width = 0, blocks = 1, conv = 1;
+  // attention side of a parallel mixer: H query heads on G key/value heads, key size `dim`, value size `vdim`, a linear
+  // distance bias per head, visibility limited to the query's own chunk of `chunk` positions (0 = whole causal prefix)
+  int heads = 0, kv_heads = 0, dim = 0, vdim = 0, chunk = 0;
+  float scale = 1.f, left_scale = 1.f;
+  // matrix-memory side (mLSTM): heads x (dim x vdim) state, gate pre-activations soft-capped at gate_cap
+  int m_heads = 0, m_dim = 0, m_vdim = 0;
+  float gate_cap = 0.f, right_scale = 1.f;
+  // feed-forward
+  int mlp = NONE;
+  int ff = 0;                                    // dense
+  int experts = 0, top = 0, expert_ff = 0, shared_ff = 0;   // mixture of experts (+ an always-on shared expert if shared_ff > 0)
+};
+
 struct ModelSpec {
-  std::string model_type;       // "opt" | "llama" | "qwen2" | "qwen3"
+  std::string model_type;       // "opt" | "llama" | "qwen2" | "qwen3" | "safupel"
+  // layer-list models (config.json "architecture"): per-layer descriptions and the multiplier of the logits
+  std::vector<HybridLayerSpec> hybrid;
+  float logit_scale = 1.f;
+  bool is_hybrid() const { return !hybrid.empty(); }
   bool qkv_bias = false;        // qwen2: q/k/v projections carry a bias
   bool qk_norm = false;         // qwen3: RMSNorm over head_dim on q and k, per head, before RoPE
   int vocab = 0, d = 0, L = 0, H = 0, KV = 0, hd = 0, ffn = 0, max_pos = 0;
@@ -26,7 +51,7 @@ struct ModelSpec {
 
 struct HostTensor {
   const uint8_t* data = nullptr;   // inside an mmap
-  std::string dtype;               // "BF16" | "F16" | "F32"
+  std::string dtype;               // "BF16" | "F16" | "F32" | "I32"
   std::vector<int64_t> shape;
   int64_t numel() const { int64_t n = 1; for (auto s : shape) n *= s; return n; }
 };
@@ -45,6 +70,8 @@ class ModelDir {
   // The same slice as bfloat16 bits (f16 = false) or IEEE half bits (f16 = true), converted from whatever the file holds.
   bool read_16(const std::string& name, int64_t r0, int64_t r1, int64_t c0, int64_t c1, bool f16,
                std::vector<uint16_t>* out, std::string* err) const;
+  // A whole tensor of any rank as 32-bit floats (BF16 / F16 / F32 widen exactly; I32 tables convert by value).
+  bool read_f32(const std::string& name, std::vector<float>* out, std::string* err) const;
 
  private:
   struct Map { void* base; size_t len; };

@@ -1,0 +1,93 @@
+// Mixture-of-experts routing: fp32 router logits, sigmoid or softmax scores, top-k choice, and the grouping of
+// (token, choice) pairs by expert that the grouped linear layer consumes.  Which rows an expert gets is all that the
+// grouping decides: a pair's result does not depend on its place in the group, and the pairs of a token are summed in
+// choice order afterwards, so the routing order never shows in the output.
+#include "common.cuh"
+#include "elt_access.cuh"
+#include "hybrid_ops.h"
+
+namespace kge {
+
+template <typename E>
+__global__ void __launch_bounds__(128) moe_score_kernel(MoeRouteArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sc_all[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= a.T) return;
+  float* sc = sc_all + warp * a.E;
+  const E* h = (const E*)a.h + (int64_t)t * a.ldh;
+  for (int e = 0; e < a.E; ++e) {
+    const E* w = (const E*)a.w_router + (int64_t)e * a.d;
+    float acc = 0.f;
+    for (int k = lane; k < a.d; k += 32) acc = fmaf(ldf(h + k), ldf(w + k), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) sc[e] = acc;
+  }
+  __syncwarp();
+  if (a.score_fn == 0) {
+    for (int e = lane; e < a.E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < a.E; e += 32) mx = fmaxf(mx, sc[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < a.E; e += 32) { const float p = expf(sc[e] - mx); sc[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < a.E; e += 32) sc[e] /= sum;
+  }
+  __syncwarp();
+  if (lane == 0) {
+    float total = 0.f;
+    for (int k = 0; k < a.top; ++k) {
+      int best = -1; float bv = -INFINITY;
+      for (int e = 0; e < a.E; ++e) {
+        bool taken = false;
+        for (int q = 0; q < k; ++q) taken |= a.choice_expert[(int64_t)t * a.top + q] == e;
+        if (!taken && sc[e] > bv) { bv = sc[e]; best = e; }
+      }
+      a.choice_expert[(int64_t)t * a.top + k] = best;
+      a.choice_weight[(int64_t)t * a.top + k] = bv;
+      total += bv;
+    }
+    if (a.renorm) for (int k = 0; k < a.top; ++k) a.choice_weight[(int64_t)t * a.top + k] /= total;
+  }
+}
+
+__global__ void __launch_bounds__(1024) moe_group_kernel(MoeRouteArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ int cnt[];            // [E] counts, then [E] cursors
+  int* cur = cnt + a.E;
+  const int n = a.T * a.top;
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[a.choice_expert[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int e = 0; e < a.E; ++e) { a.group_off[e] = off; cur[e] = off; off += cnt[e]; }
+    a.group_off[a.E] = off;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int p = atomicAdd(&cur[a.choice_expert[i]], 1);
+    a.perm_token[p] = i / a.top;
+    a.perm_weight[p] = a.choice_weight[i];
+    a.perm_dest[p] = i;
+  }
+}
+
+int moe_route(const MoeRouteArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return 0;
+  KGE_REQUIRE(a.E > 0 && a.top > 0 && a.top <= a.E && a.E <= 4096, "moe_route: %d experts, top %d", a.E, a.top);
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(moe_score_kernel<float>, dim3((a.T + 3) / 4), dim3(128), (size_t)4 * a.E * 4, st, a)
+                                        : launch_pdl(moe_score_kernel<__nv_bfloat16>, dim3((a.T + 3) / 4), dim3(128), (size_t)4 * a.E * 4, st, a);
+  KGE_CUDA_OK(ce);
+  KGE_CUDA_OK(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)2 * a.E * 4, st, a));
+  return 0;
+}
+
+}  // namespace kge

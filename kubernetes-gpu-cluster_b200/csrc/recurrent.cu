@@ -1,0 +1,188 @@
+// Recurrent token mixers with per-request state slots, in bfloat16 or float32 storage and fp32 state:
+//   - the gated linear recurrence (RG-LRU): causal per-channel convolution whose last inputs are carried in the slot,
+//     then S <- a S + sqrt(1 - a^2) i u with a = exp(-c r softplus(lam)), one thread per (request, channel);
+//   - the matrix memory (mLSTM) with a running maximum that starts at 0, one block per (request, head), the dim x vdim
+//     state in shared memory, one thread per value column.
+// A request whose first row of the step is position 0 starts from zero; otherwise from what its slot holds.  Rows of a
+// request are processed in order, so cutting a prompt into steps anywhere gives the same arithmetic.
+#include <algorithm>
+
+#include "common.cuh"
+#include "elt_access.cuh"
+#include "hybrid_ops.h"
+
+namespace kge {
+
+constexpr int MAX_TAPS = 16;
+
+template <typename E>
+__global__ void rglru_conv_kernel(RglruArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int b = a.token_req[t], pos = a.positions[t], rs = a.qsl[b];
+  const int p0 = a.positions[rs];                         // position of the request's first row in this step
+  const E* yx = (const E*)a.yx;
+  const float* tail = a.state + (int64_t)a.slots[b] * a.slot_stride + a.width;
+  for (int c = threadIdx.x; c < a.width; c += blockDim.x) {
+    float acc = ldf((const E*)a.conv_b + c);
+    for (int j = 0; j < a.taps; ++j) {
+      const int back = a.taps - 1 - j, sp = pos - back;
+      float xv = 0.f;
+      if (sp >= p0) xv = ldf(yx + (int64_t)(t - back) * 2 * a.width + a.width + c);
+      else if (sp >= 0) xv = tail[(int64_t)(sp - p0 + a.taps - 1) * a.width + c];
+      acc = fmaf(ldf((const E*)a.conv_w + (int64_t)c * a.taps + j), xv, acc);
+    }
+    stf((E*)a.u + (int64_t)t * a.width + c, acc);
+  }
+}
+
+int rglru_conv(const RglruArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return 0;
+  KGE_REQUIRE(a.taps >= 1 && a.taps <= MAX_TAPS, "rglru_conv: %d taps (1..%d)", a.taps, MAX_TAPS);
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(rglru_conv_kernel<float>, dim3(a.T), dim3(256), 0, st, a)
+                                        : launch_pdl(rglru_conv_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), 0, st, a);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + expf(-v)); }
+__device__ __forceinline__ float softplusf_(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+__device__ __forceinline__ float gelu_tanhf_(float v) { return 0.5f * v * (1.f + tanhf(0.79788456080286536f * (v + 0.044715f * v * v * v))); }
+
+template <typename E>
+__global__ void __launch_bounds__(128) rglru_scan_kernel(RglruArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.width) return;
+  const int rs = a.qsl[b], re = a.qsl[b + 1], p0 = a.positions[rs], n = re - rs;
+  float* slot = a.state + (int64_t)a.slots[b] * a.slot_stride;
+  const E* yx = (const E*)a.yx;
+  const E* u = (const E*)a.u;
+  E* out = (E*)a.out;
+  const float sp = a.decay_c * softplusf_(ldf((const E*)a.lam + c));
+  float S = p0 > 0 ? slot[c] : 0.f;
+  for (int t = rs; t < re; ++t) {
+    const float r = sigmoidf_(a.gates[(int64_t)t * 2 * a.width + c]);
+    const float i = sigmoidf_(a.gates[(int64_t)t * 2 * a.width + a.width + c]);
+    const float log_a = -sp * r;
+    const float av = expf(log_a);
+    const float mult = sqrtf(-expm1f(2.f * log_a));          // sqrt(1 - a^2) without cancellation near a = 1
+    S = fmaf(av, S, mult * i * ldf(u + (int64_t)t * a.width + c));
+    stf(out + (int64_t)t * a.width + c, S * gelu_tanhf_(ldf(yx + (int64_t)t * 2 * a.width + c)));
+  }
+  slot[c] = S;
+  // the conv's next inputs: positions p1 - (taps - 1) .. p1 - 1 with p1 = p0 + n, from this step's rows or the old tail
+  float nt[MAX_TAPS];
+  float* tail = slot + a.width;
+#pragma unroll
+  for (int k = 0; k < MAX_TAPS; ++k) {
+    if (k >= a.taps - 1) break;
+    const int sp2 = p0 + n - (a.taps - 1) + k;
+    float v = 0.f;
+    if (sp2 >= p0) v = ldf(yx + (int64_t)(rs + sp2 - p0) * 2 * a.width + a.width + c);
+    else if (sp2 >= 0) v = tail[(int64_t)(sp2 - p0 + a.taps - 1) * a.width + c];
+    nt[k] = v;
+  }
+#pragma unroll
+  for (int k = 0; k < MAX_TAPS; ++k) {
+    if (k >= a.taps - 1) break;
+    tail[(int64_t)k * a.width + c] = nt[k];
+  }
+}
+
+int rglru_scan(const RglruArgs& a, cudaStream_t st) {
+  if (a.T <= 0 || a.B <= 0) return 0;
+  KGE_REQUIRE(a.taps >= 1 && a.taps <= MAX_TAPS, "rglru_scan: %d taps (1..%d)", a.taps, MAX_TAPS);
+  const dim3 grid(a.B, (a.width + 127) / 128), block(128);
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(rglru_scan_kernel<float>, grid, block, 0, st, a)
+                                        : launch_pdl(rglru_scan_kernel<__nv_bfloat16>, grid, block, 0, st, a);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------ matrix memory
+template <typename E>
+__global__ void mlstm_step_kernel(MlstmArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int dim = a.dim, vdim = a.vdim;
+  float* S = sm;                       // [dim][vdim]
+  float* nv = S + (int64_t)dim * vdim; // [dim]
+  float* ks = nv + dim;                // [dim]
+  float* qs = ks + dim;                // [dim]
+  float* red = qs + dim;               // [33]
+  const int rs = a.qsl[b], re = a.qsl[b + 1], p0 = a.positions[rs];
+  float* slot = a.state + (int64_t)a.slots[b] * a.slot_stride + (int64_t)h * ((int64_t)dim * vdim + dim + 1);
+  const bool fresh = p0 == 0;
+  for (int i = tid; i < dim * vdim + dim; i += blockDim.x) S[i] = fresh ? 0.f : slot[i];     // S then n: contiguous in both
+  float m = fresh ? 0.f : slot[(int64_t)dim * vdim + dim];
+  __syncthreads();
+  const E *qp = (const E*)a.q, *kp = (const E*)a.k, *vp = (const E*)a.v, *gp = (const E*)a.g;
+  const float nw = tid < vdim ? ldf((const E*)a.norm_w + h * vdim + tid) : 0.f;
+  for (int t = rs; t < re; ++t) {
+    if (tid < dim) {
+      ks[tid] = ldf(kp + (int64_t)t * a.ld + h * dim + tid);
+      qs[tid] = ldf(qp + (int64_t)t * a.ld + h * dim + tid) * a.q_scale;
+    }
+    const float ip = a.gates[(int64_t)t * 2 * a.H + h], fp = a.gates[(int64_t)t * 2 * a.H + a.H + h];
+    const float it = a.cap * tanhf(ip / a.cap);
+    const float fc = a.cap * tanhf(fp / a.cap);
+    const float ft = fminf(fc, 0.f) - log1pf(expf(-fabsf(fc)));          // logsigmoid
+    const float mn = fmaxf(ft + m, it);
+    const float fa = expf(ft + m - mn), ia = expf(it - mn);
+    m = mn;
+    __syncthreads();
+    float part = 0.f;
+    if (tid < dim) {
+      const float nn = fmaf(fa, nv[tid], ia * ks[tid]);
+      nv[tid] = nn;
+      part = nn * qs[tid];
+    }
+    const float nq = block_sum(part, red);
+    float o = 0.f;
+    if (tid < vdim) {
+      const float vv = ia * ldf(vp + (int64_t)t * a.ld + h * vdim + tid);
+      float num = 0.f;
+      for (int d = 0; d < dim; ++d) {
+        const float s = fmaf(fa, S[d * vdim + tid], ks[d] * vv);
+        S[d * vdim + tid] = s;
+        num = fmaf(s, qs[d], num);
+      }
+      o = num / (fmaxf(fabsf(nq), expf(-m)) + a.den_eps);
+    }
+    const float ss = block_sum(o * o, red);
+    if (tid < vdim) {
+      const float inv = 1.f / sqrtf(ss / (float)vdim + a.eps);
+      const float gate = 1.f / (1.f + expf(-ldf(gp + (int64_t)t * a.ld + h * vdim + tid)));
+      stf((E*)a.out + (int64_t)t * a.ldo + h * vdim + tid, o * inv * nw * gate * a.out_scale);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < dim * vdim + dim; i += blockDim.x) slot[i] = S[i];
+  if (tid == 0) slot[(int64_t)dim * vdim + dim] = m;
+}
+
+int mlstm_step(const MlstmArgs& a, cudaStream_t st) {
+  if (a.T <= 0 || a.B <= 0) return 0;
+  const int threads = (std::max(a.dim, a.vdim) + 31) / 32 * 32;
+  KGE_REQUIRE(threads <= 1024, "mlstm_step: head sizes %d x %d need more than 1024 threads", a.dim, a.vdim);
+  const size_t smem = ((size_t)a.dim * a.vdim + 3 * (size_t)a.dim + 64) * 4;
+  KGE_REQUIRE(smem <= 227 * 1024, "mlstm_step: a %d x %d state does not fit shared memory", a.dim, a.vdim);
+  const dim3 grid(a.B, a.H), block(threads);
+  cudaError_t ce;
+  if (a.elt == KGE_ELT_F32) {
+    cudaFuncSetAttribute(mlstm_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ce = launch_pdl(mlstm_step_kernel<float>, grid, block, smem, st, a);
+  } else {
+    cudaFuncSetAttribute(mlstm_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ce = launch_pdl(mlstm_step_kernel<__nv_bfloat16>, grid, block, smem, st, a);
+  }
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+}  // namespace kge

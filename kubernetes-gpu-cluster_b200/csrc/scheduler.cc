@@ -77,7 +77,23 @@ void BlockPool::set_hash(int32_t b, const BlockHash& h) {
 }
 
 // ------------------------------------------------------------------------------- scheduler
-Scheduler::Scheduler(const SchedConfig& c) : cfg_(c) { pool_.init(c.num_blocks); }
+Scheduler::Scheduler(const SchedConfig& c) : cfg_(c) {
+  pool_.init(c.num_blocks);
+  if (cfg_.num_state_slots > 0) cfg_.enable_prefix_caching = false;
+  for (int32_t i = cfg_.num_state_slots - 1; i >= 0; --i) free_slots_.push_back(i);   // slot 0 is handed out first
+}
+
+bool Scheduler::take_slot(Request* r) {
+  if (cfg_.num_state_slots <= 0 || r->state_slot >= 0) return true;
+  if (free_slots_.empty()) return false;
+  r->state_slot = free_slots_.back();
+  free_slots_.pop_back();
+  return true;
+}
+void Scheduler::give_slot(Request* r) {
+  if (r->state_slot >= 0) free_slots_.push_back(r->state_slot);
+  r->state_slot = -1;
+}
 
 static inline uint64_t mix64(uint64_t x) {
   x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
@@ -199,6 +215,7 @@ void Scheduler::release(Request* r) {
   pool_.release(order);
   r->blocks.clear();
   r->num_hashed_blocks = 0;
+  give_slot(r);
 }
 
 void Scheduler::finish(Request* r, ReqStatus st) {
@@ -248,9 +265,11 @@ const std::vector<Scheduled>& Scheduler::schedule() {
   if (!preempted) {
     while (!waiting_.empty() && budget > 0) {
       if ((int32_t)running_.size() == cfg_.max_num_seqs) break;
+      if (cfg_.num_state_slots > 0 && free_slots_.empty()) break;
       Request* r = waiting_.front();
       const int32_t n = admit(r, budget);
       if (n < 0) break;
+      take_slot(r);
       waiting_.pop_front();
       r->status = ReqStatus::Running;
       running_.push_back(r);
@@ -260,6 +279,53 @@ const std::vector<Scheduled>& Scheduler::schedule() {
   }
   for (auto& s : sched_) s.req->num_computed += s.num_tokens;
   return sched_;
+}
+
+bool Scheduler::extend_prompt(int64_t id, const int32_t* tokens, int32_t n, const char** why) {
+  static const char* kUnknown = "unknown request id";
+  static const char* kOut = "the request has sampled tokens already";
+  static const char* kLong = "the request would be longer than max_model_len";
+  Request* r = find(id);
+  if (!r) { if (why) *why = kUnknown; return false; }
+  if (!r->output.empty()) { if (why) *why = kOut; return false; }
+  if (r->num_tokens() + n >= cfg_.max_model_len) { if (why) *why = kLong; return false; }
+  r->prompt.insert(r->prompt.end(), tokens, tokens + n);
+  return true;
+}
+
+bool Scheduler::schedule_scripted(const std::vector<std::pair<int64_t, int32_t>>& plan, const char** why) {
+  static const char* kUnknown = "the plan names an unknown request";
+  static const char* kTokens = "the plan runs more tokens than the request holds";
+  static const char* kBlocks = "the KV pool has too few free blocks for the plan";
+  static const char* kSlots = "no free state slot or sequence place for a new request";
+  static const char* kTwice = "the plan names a request twice";
+  sched_.clear();
+  const int32_t bs = cfg_.block_size;
+  int32_t need_blocks = 0, need_slots = 0, newcomers = 0;
+  for (size_t i = 0; i < plan.size(); ++i) {
+    Request* r = find(plan[i].first);
+    if (!r) { if (why) *why = kUnknown; return false; }
+    for (size_t k = 0; k < i; ++k) if (plan[k].first == plan[i].first) { if (why) *why = kTwice; return false; }
+    const int32_t n = plan[i].second;
+    if (n <= 0 || r->num_computed + n > r->num_tokens()) { if (why) *why = kTokens; return false; }
+    need_blocks += std::max(0, (r->num_computed + n + bs - 1) / bs - (int32_t)r->blocks.size());
+    if (r->status != ReqStatus::Running) { ++newcomers; if (cfg_.num_state_slots > 0) ++need_slots; }
+  }
+  if (need_blocks > pool_.num_free()) { if (why) *why = kBlocks; return false; }
+  if (need_slots > (int32_t)free_slots_.size() || (int32_t)running_.size() + newcomers > cfg_.max_num_seqs) { if (why) *why = kSlots; return false; }
+  for (auto& pl : plan) {
+    Request* r = find(pl.first);
+    if (r->status != ReqStatus::Running) {
+      waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), r), waiting_.end());
+      r->status = ReqStatus::Running;
+      running_.push_back(r);
+      take_slot(r);
+    }
+    alloc(r, pl.second);
+    sched_.push_back({r, pl.second});
+  }
+  for (auto& s : sched_) s.req->num_computed += s.num_tokens;
+  return true;
 }
 
 void Scheduler::update(const std::vector<int32_t>& sampled, std::vector<StepResult>* out) {

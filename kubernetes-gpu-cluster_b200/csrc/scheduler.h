@@ -50,6 +50,7 @@ struct Request {
   int32_t num_hashed_blocks = 0;         // leading entries of `blocks` that are registered in the prefix cache
   int32_t num_cached_tokens = 0;         // tokens taken from the prefix cache at the last admission
   ReqStatus status = ReqStatus::Waiting;
+  int32_t state_slot = -1;               // models with recurrent state: the slot of the state pool a RUNNING request owns
   int32_t num_preemptions = 0;
   int32_t num_tokens() const { return (int32_t)(prompt.size() + output.size()); }
   int32_t token_at(int32_t i) const {
@@ -71,6 +72,11 @@ struct SchedConfig {
   // vllm --enable-prefix-caching: full blocks stay addressable by the hash of their token prefix after their request
   // is gone, and a new request whose prompt starts with the same tokens reuses them instead of recomputing.
   bool enable_prefix_caching = false;
+  // Models with per-request recurrent state (linear recurrences, matrix memories): the size of the state pool.  A request
+  // takes a slot when it starts RUNNING and gives it back when it finishes or is preempted; a request whose first
+  // scheduled token is position 0 starts from a zero state whatever its slot held before.  0 = the model has none.
+  // Cached KV blocks cannot bring a recurrent state back, so prefix caching stays off for such models.
+  int32_t num_state_slots = 0;
 };
 
 // Fixed pool of KV blocks: free queue (doubly linked, O(1) removal from the middle), reference counts, and the
@@ -137,8 +143,21 @@ class Scheduler {
   int64_t prefix_cache_queries() const { return pc_queries_; }   // tokens looked up / tokens served from the cache
   int64_t prefix_cache_hits() const { return pc_hits_; }
   Request* find(int64_t id);
+  // Replaying a recorded trace: the caller, not the policy above, says which request runs how many tokens in a step.
+  // extend_prompt appends known tokens to a request that has not consumed all of its prompt's successors yet;
+  // schedule_scripted admits WAITING requests named in the plan (slot + blocks through the same pool), grows the
+  // others and advances them exactly as told.  Returns false, with nothing changed, when blocks or slots run out or
+  // the plan names an unknown request or more tokens than it holds.  Follow it with update({}) or finish requests
+  // through abort().
+  bool extend_prompt(int64_t id, const int32_t* tokens, int32_t n, const char** why);
+  bool schedule_scripted(const std::vector<std::pair<int64_t, int32_t>>& plan, const char** why);
+  const std::vector<Scheduled>& scheduled() const { return sched_; }
+  int32_t free_state_slots() const { return (int32_t)free_slots_.size(); }
 
  private:
+  bool take_slot(Request* r);
+  void give_slot(Request* r);
+  std::vector<int32_t> free_slots_;
   bool alloc(Request* r, int32_t n_new);
   int32_t admit(Request* r, int32_t budget);            // tokens scheduled, or -1: the request has to wait
   void release(Request* r);
