@@ -484,6 +484,18 @@ typedef struct kge_sched kge_sched;
 kge_sched* kge_sched_create(int32_t max_num_seqs, int32_t max_num_batched_tokens,
                             int32_t max_model_len, int32_t block_size, int32_t num_blocks,
                             int32_t enable_chunked_prefill, int32_t eos_token_id);
+/* Models with recurrent state: the scheduler also owns `num_state_slots` state slots; a request holds one while it is
+ * RUNNING (kge_sched_state_slot, -1 otherwise) and prefix caching stays off.  kge_sched_extend appends prompt tokens to
+ * a request that has sampled nothing yet; kge_sched_schedule_scripted runs exactly num_tokens[i] further tokens of
+ * request ids[i] (admitting it if it waits) through the same block pool and slots, or fails and changes nothing. */
+kge_sched* kge_sched_create_stateful(int32_t max_num_seqs, int32_t max_num_batched_tokens, int32_t max_model_len,
+                                     int32_t block_size, int32_t num_blocks, int32_t enable_chunked_prefill,
+                                     int32_t eos_token_id, int32_t num_state_slots);
+int kge_sched_extend(kge_sched* s, int64_t request_id, const int32_t* token_ids, int32_t n);
+int kge_sched_schedule_scripted(kge_sched* s, const int64_t* ids, const int32_t* num_tokens, int32_t n);
+int32_t kge_sched_state_slot(kge_sched* s, int64_t request_id);
+int32_t kge_sched_request_blocks(kge_sched* s, int64_t request_id, int32_t* out, int32_t cap);   /* returns the count */
+int kge_sched_abort(kge_sched* s, int64_t request_id);
 void kge_sched_destroy(kge_sched* s);
 /* vllm --scheduler-reserve-full-isl / --no-scheduler-reserve-full-isl (vllm:config/scheduler.py, default on;
  * the admission gate of vllm:v1/core/kv_cache_manager.py:346-360): a waiting request is admitted only when

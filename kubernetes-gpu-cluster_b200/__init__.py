@@ -154,6 +154,12 @@ SIGNATURES = {
     "kge_sched_schedule": (_I, [_P, _P, _P, C.c_int32]),
     "kge_sched_update": (_I, [_P, _P, _P, C.c_int32, C.POINTER(StepOutput), C.c_int32]),
     "kge_sched_counts": (_I, [_P, _P, _P, _P]),
+    "kge_sched_create_stateful": (_P, [C.c_int32] * 8),
+    "kge_sched_extend": (_I, [_P, _L, _P, C.c_int32]),
+    "kge_sched_schedule_scripted": (_I, [_P, _P, _P, C.c_int32]),
+    "kge_sched_state_slot": (C.c_int32, [_P, _L]),
+    "kge_sched_request_blocks": (C.c_int32, [_P, _L, _P, C.c_int32]),
+    "kge_sched_abort": (_I, [_P, _L]),
     "kge_trace_add": (_I, [_P, _L, _P, C.c_int32]),
     "kge_trace_step": (_I, [_P, _P, _P, C.c_int32, _P, _P, _P]),
     "kge_trace_end": (_I, [_P, _L]),

@@ -329,7 +329,7 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
     if (sampled) KGE_CUDA_OK(cudaMemcpyAsync(e->out_host, e->d_out, (size_t)R * 4, cudaMemcpyDeviceToHost, e->stream));
     if (lp_n >= 0 && sampled) {
       // raw log-probabilities of the sampled tokens (vllm:v1/sample/sampler.py:300-349), for the rows that asked
-      if (int rc = e->op->logprobs(e->lp_vals, e->lp_ids, e->lp_rank, e->logits, e->d_out, R, e->spec.vocab, e->spec.vocab, lp_n, e->stream)) return rc;
+      if (int rc = e->op->logprobs(e->lp_vals, e->lp_ids, e->lp_rank, e->logits, e->d_out, R, e->spec.vocab, hybrid ? e->ld_logits : e->spec.vocab, lp_n, e->stream)) return rc;
       ++e->launches;
       const size_t n = (size_t)R * (lp_n + 1) * 4;
       KGE_CUDA_OK(cudaMemcpyAsync(e->lp_vals_host, e->lp_vals, n, cudaMemcpyDeviceToHost, e->stream));
@@ -360,7 +360,8 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
 // engine_hybrid.cu applies the min_tokens mask through this (the kernel lives here)
 int mask_step_logits(kge_engine* e) {
   if (e->step_num_masks <= 0) return 0;
-  mask_logits_kernel<<<(e->step_num_masks + 127) / 128, 128, 0, e->stream>>>(e->logits, e->mask_pairs, e->step_num_masks, e->spec.vocab, e->spec.vocab, e->f16);
+  mask_logits_kernel<<<(e->step_num_masks + 127) / 128, 128, 0, e->stream>>>(e->logits, e->mask_pairs, e->step_num_masks,
+                                                                             e->spec.is_hybrid() ? e->ld_logits : e->spec.vocab, e->spec.vocab, e->f16);
   KGE_LAUNCH_OK();
   ++e->launches;
   pdl_break_next();
@@ -641,6 +642,43 @@ extern "C" kge_sched* kge_sched_create(int32_t max_num_seqs, int32_t max_num_bat
   k->s.reset(new Scheduler(c));
   return k;
 }
+extern "C" kge_sched* kge_sched_create_stateful(int32_t max_num_seqs, int32_t max_num_batched_tokens, int32_t max_model_len,
+                                                int32_t block_size, int32_t num_blocks, int32_t enable_chunked_prefill,
+                                                int32_t eos_token_id, int32_t num_state_slots) {
+  SchedConfig c;
+  c.max_num_seqs = max_num_seqs; c.max_num_batched_tokens = max_num_batched_tokens;
+  c.max_model_len = max_model_len; c.block_size = block_size; c.num_blocks = num_blocks;
+  c.enable_chunked_prefill = enable_chunked_prefill != 0; c.eos_token_id = eos_token_id; c.num_state_slots = num_state_slots;
+  kge_sched* k = new kge_sched();
+  k->s.reset(new Scheduler(c));
+  return k;
+}
+extern "C" int kge_sched_extend(kge_sched* s, int64_t request_id, const int32_t* token_ids, int32_t n) {
+  KGE_REQUIRE(s && token_ids && n > 0, "kge_sched_extend: bad arguments");
+  const char* why = nullptr;
+  if (!s->s->extend_prompt(request_id, token_ids, n, &why)) { kge::set_error("kge_sched_extend: %s", why ? why : "rejected"); return -1; }
+  return 0;
+}
+extern "C" int kge_sched_schedule_scripted(kge_sched* s, const int64_t* ids, const int32_t* num_tokens, int32_t n) {
+  KGE_REQUIRE(s && ids && num_tokens && n > 0, "kge_sched_schedule_scripted: bad arguments");
+  std::vector<std::pair<int64_t, int32_t>> plan;
+  for (int i = 0; i < n; ++i) plan.push_back({ids[i], num_tokens[i]});
+  const char* why = nullptr;
+  if (!s->s->schedule_scripted(plan, &why)) { kge::set_error("kge_sched_schedule_scripted: %s", why ? why : "rejected"); return -1; }
+  return 0;
+}
+extern "C" int32_t kge_sched_state_slot(kge_sched* s, int64_t request_id) {
+  Request* r = s ? s->s->find(request_id) : nullptr;
+  return r ? r->state_slot : -1;
+}
+extern "C" int32_t kge_sched_request_blocks(kge_sched* s, int64_t request_id, int32_t* out, int32_t cap) {
+  Request* r = s ? s->s->find(request_id) : nullptr;
+  if (!r) return -1;
+  const int32_t n = (int32_t)r->blocks.size();
+  for (int32_t i = 0; i < n && i < cap; ++i) out[i] = r->blocks[i];
+  return n;
+}
+extern "C" int kge_sched_abort(kge_sched* s, int64_t request_id) { return s && s->s->abort(request_id) ? 0 : -1; }
 extern "C" void kge_sched_destroy(kge_sched* s) { delete s; }
 extern "C" void kge_sched_set_reserve_full_isl(kge_sched* s, int32_t on) { if (s) s->s->set_reserve_full_isl(on != 0); }
 extern "C" void kge_engine_set_reserve_full_isl(kge_engine* e, int32_t on) { if (e && e->sched) e->sched->set_reserve_full_isl(on != 0); }

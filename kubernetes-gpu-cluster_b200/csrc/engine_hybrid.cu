@@ -400,11 +400,11 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       HFWD(linear_any(a, st));
     }
     if (R <= Rm) {
-      // the samplers read 16-bit logits
-      HFWD(logits_to_elt16(e->logits, e->logits32, R, s.vocab, s.vocab, false, st));
+      // the samplers read 16-bit logits, rows padded to the 16-byte alignment they ask for
+      HFWD(logits_to_elt16(e->logits, e->logits32, R, s.vocab, e->ld_logits, false, st));
       if (int rc = mask_step_logits(e)) return rc;
-      if (any_random) HFWD(kge_sample(e->d_out, e->logits, R, s.vocab, s.vocab, m.temp, m.top_k, m.top_p, nullptr, m.seeds, 0, nullptr, 0, st));
-      else HFWD(kge_argmax(e->d_out, e->logits, R, s.vocab, s.vocab, st));
+      if (any_random) HFWD(kge_sample(e->d_out, e->logits, R, s.vocab, e->ld_logits, m.temp, m.top_k, m.top_p, nullptr, m.seeds, 0, nullptr, 0, st));
+      else HFWD(kge_argmax(e->d_out, e->logits, R, s.vocab, e->ld_logits, st));
     }
   }
   return 0;

@@ -311,6 +311,26 @@ extern "C" void kge_model_close(kge_model_dir* m) { delete m; }
 extern "C" int kge_model_spec_json(const kge_model_dir* m, char* out, int cap) {
   KGE_REQUIRE(m && out && cap > 0, "kge_model_spec_json: bad arguments");
   const kge::ModelSpec& s = m->md.spec();
+  if (s.is_hybrid()) {
+    std::string j = "{\"model_type\":\"" + s.model_type + "\",\"vocab\":" + std::to_string(s.vocab) + ",\"d\":" + std::to_string(s.d) +
+                    ",\"L\":" + std::to_string(s.L) + ",\"has_weights\":" + (m->md.has_weights() ? "true" : "false") + ",\"layers\":[";
+    char buf[512];
+    for (size_t i = 0; i < s.hybrid.size(); ++i) {
+      const kge::HybridLayerSpec& h = s.hybrid[i];
+      snprintf(buf, sizeof buf,
+               "%s{\"mixer\":%d,\"width\":%d,\"blocks\":%d,\"conv\":%d,\"heads\":%d,\"kv_heads\":%d,\"dim\":%d,\"vdim\":%d,\"chunk\":%d,"
+               "\"scale\":%.9g,\"left_scale\":%.9g,\"right_scale\":%.9g,\"m_heads\":%d,\"m_dim\":%d,\"m_vdim\":%d,\"gate_cap\":%.9g,"
+               "\"mlp\":%d,\"ff\":%d,\"experts\":%d,\"top\":%d,\"expert_ff\":%d,\"shared_ff\":%d}",
+               i ? "," : "", h.mixer, h.width, h.blocks, h.conv, h.heads, h.kv_heads, h.dim, h.vdim, h.chunk, (double)h.scale, (double)h.left_scale,
+               (double)h.right_scale, h.m_heads, h.m_dim, h.m_vdim, (double)h.gate_cap, h.mlp, h.ff, h.experts, h.top, h.expert_ff, h.shared_ff);
+      j += buf;
+    }
+    snprintf(buf, sizeof buf, "],\"eps\":%.9g,\"logit_scale\":%.9g}", (double)s.eps, (double)s.logit_scale);
+    j += buf;
+    KGE_REQUIRE((int)j.size() < cap, "kge_model_spec_json: buffer of %d bytes too small", cap);
+    memcpy(out, j.c_str(), j.size() + 1);
+    return (int)j.size();
+  }
   const int n = snprintf(out, (size_t)cap,
                          "{\"model_type\":\"%s\",\"qkv_bias\":%s,\"qk_norm\":%s,\"vocab\":%d,\"d\":%d,\"L\":%d,\"H\":%d,\"KV\":%d,\"hd\":%d,"
                          "\"ffn\":%d,\"max_pos\":%d,\"eps\":%.9g,\"tied\":%s,\"rope_theta\":%.17g,\"rope_factor\":%.17g,\"rope_low\":%.17g,"
