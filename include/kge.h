@@ -97,7 +97,7 @@ int kge_layernorm(void* y, void* residual, const void* add, const void* w, const
 int kge_silu_mul(void* y, const void* x, int T, int f, void* stream);
 
 /* Dense projection y[T,N] = act(x[T,K] * w[N,K]^T + bias[N]); bf16 in/out, fp32 accumulate,
- * one rounding.  act: 0 none, 1 relu.  Replaces F.linear in QKV/O/MLP/LM-head
+ * one rounding.  act: 0 none, 1 relu, 3 exact (erf) gelu.  Replaces F.linear in QKV/O/MLP/LM-head
  * (vllm:model_executor/models/llama.py:94-121,164-180; opt.py:92-106,151-165;
  * layers/logits_processor.py:89-99).  tcgen05/TMEM/TMA kernel; K % 8 == 0 (16-byte rows; a partial last
  * 64-wide k-block is zero-filled by TMA), x and w 16-byte aligned.
@@ -329,7 +329,7 @@ int kge_step(kge_engine* e, const kge_step_batch* batch, int32_t* out_ids_host,
  * 0 gemm (T<=256: weight streaming), 1 gemm (T>256: tensor bound), 2 decode attention,
  * 3 general (prefill / mixed) attention, 4 norms, 5 rope+kv write, 6 activation, 7 embed/gather,
  * 8 sampling, 9 all-reduce.  Timing adds event overhead: never enable it for a headline number. */
-#define KGE_NUM_KERNEL_CATS 10
+#define KGE_NUM_KERNEL_CATS 13     /* layer-list models add: 10 gated linear recurrence, 11 matrix memory, 12 expert routing + grouped experts */
 typedef struct {
   int64_t launches;
   double ms;          /* summed device time of the launches            */

@@ -64,9 +64,9 @@ class KernelStats(C.Structure):
     _fields_ = [("launches", C.c_int64), ("ms", C.c_double), ("bytes", C.c_double), ("flops", C.c_double)]
 
 
-NUM_KERNEL_CATS = 10
+NUM_KERNEL_CATS = 13
 KERNEL_CATS = ["gemm_decode", "gemm_prefill", "attn_decode", "attn_general", "norm", "rope_kvwrite",
-               "activation", "embed_gather", "sampling", "all_reduce"]
+               "activation", "embed_gather", "sampling", "all_reduce", "linear_recurrence", "matrix_memory", "moe_experts"]
 
 # name -> (restype, argtypes); every symbol include/kge.h declares
 _P, _I, _L, _F = C.c_void_p, C.c_int, C.c_int64, C.c_float

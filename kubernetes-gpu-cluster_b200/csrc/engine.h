@@ -95,6 +95,8 @@ struct kge_engine {
   int32_t *moe_goff = nullptr, *moe_ptok = nullptr, *moe_pdest = nullptr, *moe_cexp = nullptr;
   float *moe_pw = nullptr, *moe_cw = nullptr;
   int64_t slot_stride = 0;                   // floats per state slot
+  bool hyb_head_tc = false;                  // the LM head runs on the tensor-core GEMM (bfloat16, 16-byte rows)
+  bool want_logits32 = false;                // this step's caller reads the logits back in fp32
   float* layer_dump_host = nullptr;          // diagnostics: residual stream after every layer of the next steps
   int64_t layer_dump_cap = 0;
   const kge::Ops* op = &kge::kOpsBf16;
@@ -197,6 +199,8 @@ StepMeta carve_meta(uint8_t* base, int T, int B, int R, int max_blocks, int64_t*
 // engine_hybrid.cu: weights, arena, caches, state pool and scheduler of a layer-list model; its forward pass
 int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, std::string* err);
 int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const StepMeta& m, bool any_random);
+void timer_begin(kge_engine* e, int cat, double bytes, double flops);   // engine_fwd.cu: per-launch CUDA-event timing
+void timer_end(kge_engine* e);
 int mask_step_logits(kge_engine* e);                       // engine_fwd.cu: the step's min_tokens bans on e->logits
 void fill_uniform(void* p, int64_t n, uint64_t seed, float scale, bool f16, cudaStream_t st);   // engine.cu (16-bit storage)
 void fill_const(void* p, int64_t n, float v, bool f16, cudaStream_t st);

@@ -13,7 +13,7 @@ using namespace kge;
 
 namespace kge {
 
-static void timer_begin(kge_engine* e, int cat, double bytes, double flops) {
+void timer_begin(kge_engine* e, int cat, double bytes, double flops) {
   if (!e->timing) return;
   const size_t idx = e->ev_cat.size() * 2;
   while (e->ev_pool.size() < idx + 2) {
@@ -26,7 +26,7 @@ static void timer_begin(kge_engine* e, int cat, double bytes, double flops) {
   e->ev_work_flops.push_back(flops);
   cudaEventRecord(e->ev_pool[idx], e->stream);
 }
-static void timer_end(kge_engine* e) {
+void timer_end(kge_engine* e) {
   if (!e->timing) return;
   cudaEventRecord(e->ev_pool[e->ev_cat.size() * 2 - 1], e->stream);
 }
@@ -317,6 +317,7 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
   e->h2d_bytes += bytes;
   e->d2h_bytes += (int64_t)R * 4;
   if (hybrid) {
+    e->want_logits32 = out_logits_host != nullptr;
     if (int rc = hybrid_forward(e, T, B, R, stride, dm, any_random)) return rc;
   } else if (decode_only && max_q == 1) {
     if (int rc = engine_decode_step(e, B, stride, max_seq, dm, any_random, sum_seq)) return rc;

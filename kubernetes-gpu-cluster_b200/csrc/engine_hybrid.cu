@@ -171,8 +171,9 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
       HB_OK(L.e_down = b.mat(dn, ld, h.expert_ff, ws));
       if (h.shared_ff > 0) {
         L.s_gate.N = L.s_up.N = h.shared_ff; L.s_gate.K = L.s_up.K = d; L.s_down.N = d; L.s_down.K = h.shared_ff;
-        HB_OK(L.s_gate.w = b.mat({fp + "shared.gate"}, {h.shared_ff}, d, ws));
-        HB_OK(L.s_up.w = b.mat({fp + "shared.up"}, {h.shared_ff}, d, ws));
+        // [gate | up] in one matrix: what the fused gated GEMM reads; the generic kernel takes the two halves
+        HB_OK(L.s_gate.w = b.mat({fp + "shared.gate", fp + "shared.up"}, {h.shared_ff, h.shared_ff}, d, ws));
+        L.s_up.w = (uint8_t*)L.s_gate.w + (int64_t)h.shared_ff * d * b.esz();
         HB_OK(L.s_down.w = b.mat({fp + "shared.down"}, {d}, h.shared_ff, ws));
         max_ff = std::max(max_ff, h.shared_ff);
       }
@@ -183,7 +184,10 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   e->slot_stride = std::max<int64_t>(state_floats, 1);
 
   const int Tm = e->cfg.max_num_batched_tokens, Rm = e->cfg.max_num_seqs, es = b.esz();
-  e->ld_logits = (int)align_up64(s.vocab, 64);
+  // 16-bit logits rows: straight out of the tensor-core GEMM when its shapes allow (then the row stride is the
+  // vocabulary), else converted from fp32 into rows padded to the samplers' 16-byte alignment
+  e->hyb_head_tc = !e->f32 && s.vocab % 8 == 0 && d % 8 == 0;
+  e->ld_logits = e->hyb_head_tc ? s.vocab : (int)align_up64(s.vocab, 64);
   e->vocab_shard = e->vocab_loc = s.vocab; e->vocab_col0 = 0;
   auto aalloc = [&](int64_t elems, int esz) -> void* { return b.dalloc(elems, esz); };
   e->res32 = (float*)aalloc((int64_t)Tm * d, 4);
@@ -195,10 +199,10 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   e->obuf2 = aalloc((int64_t)Tm * d, es);
   e->ffbuf = aalloc((int64_t)Tm * max_ff, es);
   e->gates32 = (float*)aalloc((int64_t)Tm * max_gate, 4);
-  e->hsel = aalloc((int64_t)Rm * d, es);
+  e->hsel = aalloc((int64_t)std::max(Rm, Tm) * d, es);
   // logits rows: the sampled rows of a step, or every row a trace asks for
   e->logits32 = (float*)aalloc((int64_t)std::max(Rm, Tm) * s.vocab, 4);
-  e->logits = (bf16*)aalloc((int64_t)Rm * e->ld_logits, 2);
+  e->logits = (bf16*)aalloc((int64_t)std::max(Rm, Tm) * e->ld_logits, 2);
   e->state = (float*)aalloc((int64_t)Rm * e->slot_stride, 4);
   if (max_top > 0) {
     const int64_t np = (int64_t)Tm * max_top;
@@ -275,136 +279,178 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   return 0;
 }
 
-#define HFWD(call)            \
-  do {                        \
-    int _rc = (call);         \
-    if (_rc) return _rc;      \
-    ++e->launches;            \
+enum { C_GEMM_S = 0, C_GEMM_L = 1, C_ATT_DEC = 2, C_ATT_GEN = 3, C_NORM = 4, C_KVW = 5, C_ACT = 6, C_EMBED = 7, C_SAMPLE = 8, C_RGLRU = 10, C_MLSTM = 11, C_MOE = 12 };
+
+#define HFWD(cat, bytes, flops, call)      \
+  do {                                     \
+    timer_begin(e, cat, bytes, flops);     \
+    int _rc = (call);                      \
+    if (_rc) return _rc;                   \
+    timer_end(e);                          \
+    ++e->launches;                         \
   } while (0)
 
-// y[T, N] = act(x[T, K] w^T + b) in the engine's storage type (fp32 output where asked)
+// y[T, N] = act(x[T, K] w^T + b) in the engine's storage type (fp32 output where asked).  bfloat16 engines send every
+// shape the tensor-core GEMM takes (16-byte rows, packed operands) there; the rest, and float32 engines, run the
+// shape-agnostic kernel.
 static int dense(kge_engine* e, void* y, int ldy, const void* x, int ldx, const HybMat& m, int T, int act, bool out_f32 = false) {
+  if (!e->f32 && !out_f32 && m.K % 8 == 0 && ldx == m.K && ldy == m.N && (act == ACT_NONE || act == ACT_GELU_ERF) &&
+      ((uintptr_t)x & 15) == 0 && ((uintptr_t)m.w & 15) == 0)
+    return kge_gemm_bf16(y, x, m.w, m.b, T, m.N, m.K, act == ACT_GELU_ERF ? 3 : 0, nullptr, 0, e->stream);
   LinearArgs a;
   a.x = x; a.ldx = ldx; a.w = m.w; a.bias = m.b; a.y = y; a.ldy = ldy; a.T = T; a.N = m.N; a.K = m.K; a.act = act;
   a.elt = e->f32 ? KGE_ELT_F32 : KGE_ELT_BF16; a.out_f32 = out_f32 || e->f32;
   return linear_any(a, e->stream);
 }
+#define DENSE(y, ldy, x, ldx, m, T, act)                                                                    \
+  HFWD((T) <= 256 ? C_GEMM_S : C_GEMM_L, es * ((double)(m).N * (m).K + (double)(T) * ((m).K + (m).N)), \
+       2.0 * (T) * (double)(m).N * (m).K, dense(e, y, ldy, x, ldx, m, T, act))
 
 int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const StepMeta& m, bool any_random) {
   const ModelSpec& s = e->spec;
-  const int d = s.d, elt = e->f32 ? KGE_ELT_F32 : KGE_ELT_BF16, es = e->f32 ? 4 : 2, bs = e->cfg.block_size;
+  const int d = s.d, elt = e->f32 ? KGE_ELT_F32 : KGE_ELT_BF16, bs = e->cfg.block_size;
+  const double es = e->f32 ? 4 : 2;
   cudaStream_t st = e->stream;
-  auto at = [&](void* base, int64_t elems) -> void* { return (uint8_t*)base + elems * es; };
-  HFWD(embed_f32(e->res32, m.ids, e->embed, T, d, elt, st));
+  auto at = [&](void* base, int64_t elems) -> void* { return (uint8_t*)base + elems * (int64_t)es; };
+  const double Td = (double)T * d;
+  // keys a query sees, summed over the step's rows, for the attention roofline: host-side copy of the step's layout
+  const uint8_t* hostm = e->meta_host;
+  const StepMeta hm = carve_meta(const_cast<uint8_t*>(hostm), T, B, R, max_blocks, nullptr);
+  bool decode_only = true;
+  for (int i = 0; i < B; ++i) decode_only &= hm.qsl[i + 1] - hm.qsl[i] == 1;
+  HFWD(C_EMBED, Td * (es + 4), 0, embed_f32(e->res32, m.ids, e->embed, T, d, elt, st));
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
     const HybridLayerW& L = e->hyb[i];
-    HFWD(rmsnorm_f32in(e->hx, e->res32, nullptr, L.norm1, T, d, s.eps, 1.f, elt, st));
+    HFWD(C_NORM, Td * (4 + es), 0, rmsnorm_f32in(e->hx, e->res32, nullptr, L.norm1, T, d, s.eps, 1.f, 1.f, elt, st));
     CombineArgs cb;
     auto add_src = [&](const void* p, int ld, float scale) { cb.src[cb.n] = p; cb.ld[cb.n] = ld; cb.scale[cb.n] = scale; ++cb.n; };
     auto flush = [&]() -> int { if (cb.n == 0) return 0; int rc = residual_combine(e->res32, cb, T, d, elt, st); cb = CombineArgs(); return rc; };
     if (h.mixer == HybridLayerSpec::RGLRU) {
       const int w = h.width, bw = w / h.blocks;
-      HFWD(dense(e, e->pbuf, 2 * w, e->hx, d, L.yx, T, ACT_NONE));
+      DENSE(e->pbuf, 2 * w, e->hx, d, L.yx, T, ACT_NONE);
       RglruArgs ra;
       ra.yx = e->pbuf; ra.u = e->ubuf; ra.gates = e->gates32; ra.out = e->mixbuf;
       ra.conv_w = L.conv_w; ra.conv_b = L.conv_b; ra.lam = L.lam;
       ra.state = e->state + L.state_off; ra.slot_stride = e->slot_stride;
       ra.slots = m.sslot; ra.qsl = m.qsl; ra.positions = m.pos; ra.token_req = m.treq;
       ra.B = B; ra.T = T; ra.width = w; ra.taps = h.conv; ra.decay_c = 8.f; ra.elt = elt;
-      HFWD(rglru_conv(ra, st));
+      const double Tw = (double)T * w;
+      HFWD(C_RGLRU, Tw * 2 * es, 0, rglru_conv(ra, st));
       for (int gsel = 0; gsel < 2; ++gsel) {           // block-diagonal gate projections of u, kept in fp32
         const HybMat& gm = gsel ? L.ri : L.ra;
         LinearArgs a;
         a.x = e->ubuf; a.ldx = w; a.w = gm.w; a.bias = gm.b; a.y = e->gates32 + (int64_t)gsel * w; a.ldy = 2 * w;
         a.T = T; a.N = bw; a.K = bw; a.nz = h.blocks; a.x_zs = bw; a.w_zs = (int64_t)bw * bw; a.b_zs = bw; a.y_zs = bw;
         a.elt = elt; a.out_f32 = true;
-        HFWD(linear_any(a, st));
+        HFWD(C_RGLRU, Tw * (es + 4) + (double)w * bw * es, 2.0 * Tw * bw, linear_any(a, st));
       }
-      HFWD(rglru_scan(ra, st));
-      HFWD(dense(e, e->obuf1, d, e->mixbuf, w, L.o, T, ACT_NONE));
+      HFWD(C_RGLRU, Tw * (3 * es + 8) + 2.0 * B * rglru_state_floats(w, h.conv) * 4, 0, rglru_scan(ra, st));
+      DENSE(e->obuf1, d, e->mixbuf, w, L.o, T, ACT_NONE);
       add_src(e->obuf1, d, 1.f);
     } else {
       const int ka = h.heads * h.vdim, ko = L.o2.K, ldp = L.proj.N;
-      HFWD(dense(e, e->pbuf, ldp, e->hx, d, L.proj, T, ACT_NONE));
-      HFWD(dense(e, e->gates32, 2 * h.m_heads, e->hx, d, L.gates, T, ACT_NONE, true));
-      HFWD(kv_write_any(at(e->pbuf, L.off_k), ldp, at(e->pbuf, L.off_v), ldp, m.slots, L.kc, L.vc, T, h.kv_heads, h.dim, h.vdim, bs, elt, st));
+      DENSE(e->pbuf, ldp, e->hx, d, L.proj, T, ACT_NONE);
+      {
+        LinearArgs a;      // gate pre-activations of the matrix memory stay in fp32
+        a.x = e->hx; a.ldx = d; a.w = L.gates.w; a.bias = L.gates.b; a.y = e->gates32; a.ldy = 2 * h.m_heads; a.T = T; a.N = 2 * h.m_heads; a.K = d;
+        a.elt = elt; a.out_f32 = true;
+        HFWD(C_MLSTM, Td * es, 4.0 * Td * h.m_heads, linear_any(a, st));
+      }
+      HFWD(C_KVW, 2.0 * T * h.kv_heads * (h.dim + h.vdim) * es, 0,
+           kv_write_any(at(e->pbuf, L.off_k), ldp, at(e->pbuf, L.off_v), ldp, m.slots, L.kc, L.vc, T, h.kv_heads, h.dim, h.vdim, bs, elt, st));
       AttnBiasArgs aa;
       aa.q = e->pbuf; aa.ldq = ldp; aa.out = e->mixbuf; aa.ldo = ko; aa.k_cache = L.kc; aa.v_cache = L.vc;
       aa.block_table = m.btab; aa.max_blocks = max_blocks; aa.seq_lens = m.seq_lens; aa.qsl = m.qsl; aa.positions = m.pos; aa.token_req = m.treq;
       aa.B = B; aa.T = T; aa.H = h.heads; aa.G = h.kv_heads; aa.dim = h.dim; aa.vdim = h.vdim; aa.block_size = bs; aa.chunk = h.chunk;
       aa.scale = h.scale; aa.bias_span = 8.f; aa.out_scale = h.left_scale; aa.elt = elt;
-      HFWD(attn_bias_chunk(aa, st));
+      double keys = 0;                                   // visible keys over all rows
+      for (int t = 0; t < T; ++t) keys += h.chunk > 0 ? hm.pos[t] % h.chunk + 1 : hm.pos[t] + 1;
+      HFWD(decode_only ? C_ATT_DEC : C_ATT_GEN, (decode_only ? keys : (double)T) * h.kv_heads * (h.dim + h.vdim) * es + (double)T * h.heads * (h.dim + h.vdim) * es,
+           2.0 * keys * h.heads * (h.dim + h.vdim), attn_bias_chunk(aa, st));
       MlstmArgs ma;
       ma.q = at(e->pbuf, L.off_mq); ma.k = at(e->pbuf, L.off_mk); ma.v = at(e->pbuf, L.off_mv); ma.g = at(e->pbuf, L.off_mg); ma.ld = ldp;
       ma.gates = e->gates32; ma.norm_w = L.m_norm; ma.out = at(e->mixbuf, ka); ma.ldo = ko;
       ma.state = e->state + L.state_off; ma.slot_stride = e->slot_stride; ma.slots = m.sslot; ma.qsl = m.qsl; ma.positions = m.pos;
       ma.B = B; ma.T = T; ma.H = h.m_heads; ma.dim = h.m_dim; ma.vdim = h.m_vdim;
       ma.cap = h.gate_cap; ma.q_scale = 1.f / sqrtf((float)h.m_dim); ma.eps = s.eps; ma.den_eps = 1e-6f; ma.out_scale = h.right_scale; ma.elt = elt;
-      HFWD(mlstm_step(ma, st));
-      HFWD(dense(e, e->obuf1, d, e->mixbuf, ko, L.o2, T, ACT_NONE));
+      HFWD(C_MLSTM, 2.0 * B * mlstm_state_floats(h.m_heads, h.m_dim, h.m_vdim) * 4 + (double)T * h.m_heads * (2 * h.m_dim + 3 * h.m_vdim) * es,
+           4.0 * T * h.m_heads * (double)h.m_dim * h.m_vdim, mlstm_step(ma, st));
+      DENSE(e->obuf1, d, e->mixbuf, ko, L.o2, T, ACT_NONE);
       add_src(e->obuf1, d, 1.f);
     }
     if (h.mlp == HybridLayerSpec::DENSE) {
-      HFWD(dense(e, e->ffbuf, h.ff, e->hx, d, L.up, T, ACT_GELU_ERF));
-      HFWD(dense(e, e->obuf2, d, e->ffbuf, h.ff, L.down, T, ACT_NONE));
+      DENSE(e->ffbuf, h.ff, e->hx, d, L.up, T, ACT_GELU_ERF);
+      DENSE(e->obuf2, d, e->ffbuf, h.ff, L.down, T, ACT_NONE);
       add_src(e->obuf2, d, 1.f);
     } else if (h.mlp == HybridLayerSpec::MOE) {
       MoeRouteArgs ra;
       ra.h = e->hx; ra.ldh = d; ra.w_router = L.router.w; ra.T = T; ra.d = d; ra.E = h.experts; ra.top = h.top; ra.score_fn = 0; ra.renorm = false;
       ra.group_off = e->moe_goff; ra.perm_token = e->moe_ptok; ra.perm_weight = e->moe_pw; ra.perm_dest = e->moe_pdest;
       ra.choice_expert = e->moe_cexp; ra.choice_weight = e->moe_cw; ra.elt = elt;
-      HFWD(moe_route(ra, st));
+      HFWD(C_MOE, Td * es + (double)h.experts * d * es, 2.0 * Td * h.experts, moe_route(ra, st));
       ++e->launches;
       const int np = T * h.top;
+      const double wexp = (double)std::min(h.experts, np) * h.expert_ff * d * es;      // weights of the experts that are touched (at most)
       LinearArgs g;      // experts' gated front half on the gathered, weighted rows
       g.x = e->hx; g.ldx = d; g.w = L.e_gate; g.w2 = L.e_up; g.y = e->moe_hidden; g.ldy = h.expert_ff; g.T = np; g.N = h.expert_ff; g.K = d;
       g.nz = h.experts; g.w_zs = (int64_t)h.expert_ff * d; g.group_off = e->moe_goff; g.max_rows = np; g.xrows = e->moe_ptok; g.row_scale = e->moe_pw;
       g.elt = elt; g.out_f32 = e->f32;
-      HFWD(linear_any(g, st));
+      HFWD(C_MOE, 2 * wexp + (double)np * (d + h.expert_ff) * es, 4.0 * np * (double)h.expert_ff * d, linear_any(g, st));
       LinearArgs dn;     // experts' down projection, scattered to row (token * top + choice)
       dn.x = e->moe_hidden; dn.ldx = h.expert_ff; dn.w = L.e_down; dn.y = e->moe_out; dn.ldy = d; dn.T = np; dn.N = d; dn.K = h.expert_ff;
       dn.nz = h.experts; dn.w_zs = (int64_t)d * h.expert_ff; dn.group_off = e->moe_goff; dn.max_rows = np; dn.yrows = e->moe_pdest;
       dn.elt = elt; dn.out_f32 = e->f32;
-      HFWD(linear_any(dn, st));
+      HFWD(C_MOE, wexp + (double)np * (d + h.expert_ff) * es, 2.0 * np * (double)h.expert_ff * d, linear_any(dn, st));
       if (h.shared_ff > 0) {
-        LinearArgs sg;
-        sg.x = e->hx; sg.ldx = d; sg.w = L.s_gate.w; sg.w2 = L.s_up.w; sg.y = e->ffbuf; sg.ldy = h.shared_ff; sg.T = T; sg.N = h.shared_ff; sg.K = d;
-        sg.elt = elt; sg.out_f32 = e->f32;
-        HFWD(linear_any(sg, st));
-        HFWD(dense(e, e->obuf2, d, e->ffbuf, h.shared_ff, L.s_down, T, ACT_NONE));
+        const int f = h.shared_ff;
+        const double gb = es * (2.0 * f * d + (double)T * (d + f)), gf = 4.0 * T * (double)f * d;
+        if (!e->f32 && f % 64 == 0 && d % 8 == 0) {
+          // [T, 2f] never reaches memory: SiLU * mul in the epilogue of the tensor-core GEMM
+          HFWD(T <= 256 ? C_GEMM_S : C_GEMM_L, gb, gf, kge_gemm_silu_gate_ws_bf16(e->ffbuf, e->hx, L.s_gate.w, T, f, d, nullptr, 0, st));
+        } else {
+          LinearArgs sg;
+          sg.x = e->hx; sg.ldx = d; sg.w = L.s_gate.w; sg.w2 = L.s_up.w; sg.y = e->ffbuf; sg.ldy = f; sg.T = T; sg.N = f; sg.K = d;
+          sg.elt = elt; sg.out_f32 = e->f32;
+          HFWD(T <= 256 ? C_GEMM_S : C_GEMM_L, gb, gf, linear_any(sg, st));
+        }
+        DENSE(e->obuf2, d, e->ffbuf, f, L.s_down, T, ACT_NONE);
       }
       // sum in a fixed order: mixer, the token's experts by choice, the shared expert
       for (int k = 0; k < h.top; ++k) {
-        if (cb.n == 4) HFWD(flush());
+        if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush());
         add_src(at(e->moe_out, (int64_t)k * d), h.top * d, 1.f);
       }
-      if (h.shared_ff > 0) { if (cb.n == 4) HFWD(flush()); add_src(e->obuf2, d, 1.f); }
+      if (h.shared_ff > 0) { if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush()); add_src(e->obuf2, d, 1.f); }
     }
-    HFWD(flush());
+    { const double nsrc = cb.n; HFWD(C_ACT, Td * (8 + nsrc * es), 0, flush()); }
     if (e->layer_dump_host && (int64_t)(i + 1) * T * d <= e->layer_dump_cap) {
       KGE_CUDA_OK(cudaMemcpyAsync(e->layer_dump_host + (int64_t)i * T * d, e->res32, (size_t)T * d * 4, cudaMemcpyDeviceToHost, st));
       KGE_CUDA_OK(cudaStreamSynchronize(st));
     }
   }
   if (R > 0) {
-    KGE_REQUIRE(R <= std::max(e->cfg.max_num_seqs, e->cfg.max_num_batched_tokens), "hybrid_forward: %d logits rows", R);
-    // norm and head for the asked rows only, in pieces of max_num_seqs rows (the size of the gathered-row buffer)
     const int Rm = e->cfg.max_num_seqs;
-    for (int r0 = 0; r0 < R; r0 += Rm) {
-      const int n = std::min(Rm, R - r0);
-      HFWD(rmsnorm_f32in(e->hsel, e->res32, m.rows + r0, e->final_w, n, d, s.eps, 1.f, elt, st));
+    KGE_REQUIRE(R <= std::max(Rm, e->cfg.max_num_batched_tokens), "hybrid_forward: %d logits rows", R);
+    const double hb = es * ((double)s.vocab * d + (double)R * (d + s.vocab)), hf = 2.0 * R * (double)s.vocab * d;
+    if (e->hyb_head_tc) {
+      // norm (the logits' multiplier folded into it), then the tensor-core GEMM straight into the 16-bit logits
+      HFWD(C_NORM, (double)R * d * (4 + es), 0, rmsnorm_f32in(e->hsel, e->res32, m.rows, e->final_w, R, d, s.eps, 1.f, s.logit_scale, elt, st));
+      HFWD(R <= 256 ? C_GEMM_S : C_GEMM_L, hb, hf, kge_gemm_bf16(e->logits, e->hsel, e->lm_head, nullptr, R, s.vocab, d, 0, nullptr, 0, st));
+      if (e->want_logits32) HFWD(C_SAMPLE, (double)R * s.vocab * 6, 0, elt16_to_f32(e->logits32, e->logits, (int64_t)R * s.vocab, st));
+    } else {
+      HFWD(C_NORM, (double)R * d * (4 + es), 0, rmsnorm_f32in(e->hsel, e->res32, m.rows, e->final_w, R, d, s.eps, 1.f, 1.f, elt, st));
       LinearArgs a;
-      a.x = e->hsel; a.ldx = d; a.w = e->lm_head; a.y = e->logits32 + (int64_t)r0 * s.vocab; a.ldy = s.vocab; a.T = n; a.N = s.vocab; a.K = d;
+      a.x = e->hsel; a.ldx = d; a.w = e->lm_head; a.y = e->logits32; a.ldy = s.vocab; a.T = R; a.N = s.vocab; a.K = d;
       a.alpha = s.logit_scale; a.elt = elt; a.out_f32 = true;
-      HFWD(linear_any(a, st));
+      HFWD(R <= 256 ? C_GEMM_S : C_GEMM_L, hb, hf, linear_any(a, st));
+      // the samplers read 16-bit logits, rows padded to the 16-byte alignment they ask for
+      if (R <= Rm) HFWD(C_SAMPLE, (double)R * s.vocab * 6, 0, logits_to_elt16(e->logits, e->logits32, R, s.vocab, e->ld_logits, false, st));
     }
     if (R <= Rm) {
-      // the samplers read 16-bit logits, rows padded to the 16-byte alignment they ask for
-      HFWD(logits_to_elt16(e->logits, e->logits32, R, s.vocab, e->ld_logits, false, st));
       if (int rc = mask_step_logits(e)) return rc;
-      if (any_random) HFWD(kge_sample(e->d_out, e->logits, R, s.vocab, e->ld_logits, m.temp, m.top_k, m.top_p, nullptr, m.seeds, 0, nullptr, 0, st));
-      else HFWD(kge_argmax(e->d_out, e->logits, R, s.vocab, e->ld_logits, st));
+      if (any_random) HFWD(C_SAMPLE, (double)R * s.vocab * 2, 0, kge_sample(e->d_out, e->logits, R, s.vocab, e->ld_logits, m.temp, m.top_k, m.top_p, nullptr, m.seeds, 0, nullptr, 0, st));
+      else HFWD(C_SAMPLE, (double)R * s.vocab * 2, 0, kge_argmax(e->d_out, e->logits, R, s.vocab, e->ld_logits, st));
     }
   }
   return 0;

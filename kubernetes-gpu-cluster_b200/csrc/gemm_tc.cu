@@ -119,6 +119,14 @@ struct GemmParams {
   unsigned long long* trace; // phase timestamps, 16 per CTA (tools/gemm_trace.py); null outside that tool
 };
 
+// epilogue activation of the plain projection: 0 none, 1 relu, 3 exact (erf) gelu; 2 marks the gated pair internally
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) return fmaxf(v, 0.f);
+  if (act == 3) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  return v;
+}
+
+
 // One %globaltimer stamp of this CTA's phase `slot` (see tools/gemm_trace.py for the slot list).
 __device__ __forceinline__ void trace_stamp(const GemmParams& p, int slot) {
   if (p.trace) {
@@ -486,7 +494,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                   if (GATED) o[k] = silu_gate_bf16(a[ci][k], u[ci][k]);
-                  else { o[k] = a[ci][k] + bv4[k]; if (p.act == 1) o[k] = fmaxf(o[k], 0.f); }
+                  else { o[k] = a[ci][k] + bv4[k]; o[k] = apply_act(o[k], p.act); }
                 }
                 bf16* dst = p.y + (int64_t)t * p.N + n0;
                 if (vec) {
@@ -513,7 +521,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
               const int t = t0 + c + j;
               if (t < p.T) {
                 float v = __uint_as_float(r[j]) + bv;
-                if (p.act == 1) v = fmaxf(v, 0.f);
+                v = apply_act(v, p.act);
                 p.y[(int64_t)t * p.N + n] = f2bf(v);
               }
             }
@@ -611,7 +619,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
               a[k] = silu_gate_bf16(a[k], u[k]);
             } else {
               if (p.bias && n0 + k < p.N) a[k] += bf2f(p.bias[n0 + k]);
-              if (p.act == 1) a[k] = fmaxf(a[k], 0.f);
+              a[k] = apply_act(a[k], p.act);
             }
           }
           bf16* dst = p.y + (int64_t)t * p.N + n0;
@@ -794,7 +802,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         } else {
           const int n = n0 + u * UNIT + j;
           float v = a[j] + ((p.bias && n < p.N) ? bf2f(p.bias[n]) : 0.f);
-          if (p.act == 1) v = fmaxf(v, 0.f);
+          v = apply_act(v, p.act);
           o[j] = v;
         }
       }
@@ -1254,7 +1262,7 @@ extern "C" int KGE_GEMM_NAME(void* y, const void* x, const void* w, const void* 
   KGE_REQUIRE(y && x && w, "kge_gemm_bf16: null pointer");
   KGE_REQUIRE(T >= 0 && N > 0 && K > 0 && K % 8 == 0, "kge_gemm_bf16: K=%d must be a positive multiple of 8", K);
   KGE_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "kge_gemm_bf16: x and w must be 16-byte aligned");
-  KGE_REQUIRE(act == 0 || act == 1, "kge_gemm_bf16: act=%d unsupported", act);
+  KGE_REQUIRE(act == 0 || act == 1 || act == 3, "kge_gemm_bf16: act=%d unsupported (0 none, 1 relu, 3 gelu)", act);
   if (T == 0) return 0;
   bool use_ws = workspace && tunable(TUN_GEMM_WS);          // stream-K through the caller's scratch, if it is large enough
   if (use_ws) {

@@ -38,13 +38,15 @@ int linear_any(const LinearArgs& a, cudaStream_t st);
 
 // res[t, :] = float(table[ids[t], :])
 int embed_f32(float* res, const int32_t* ids, const void* table, int T, int d, int elt, cudaStream_t st);
-// y[r, :] = x[rows ? rows[r] : r, :] / sqrt(mean(x^2) + eps) * (offset + w), x fp32, y in elt
-int rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, int elt, cudaStream_t st);
+// y[r, :] = out_scale * x[rows ? rows[r] : r, :] / sqrt(mean(x^2) + eps) * (offset + w), x fp32, y in elt
+int rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, float out_scale, int elt,
+                  cudaStream_t st);
 // res[t, :] += sum_i scale[i] * src[i][t, :]   (up to 4 sources in elt, each [T, d] with its own leading dimension)
 struct CombineArgs { const void* src[4] = {nullptr, nullptr, nullptr, nullptr}; int ld[4] = {0, 0, 0, 0}; float scale[4] = {0, 0, 0, 0}; int n = 0; };
 int residual_combine(float* res, const CombineArgs& a, int T, int d, int elt, cudaStream_t st);
 // fp32 [R, V] -> 16-bit logits for the samplers (ld_out >= V)
 int logits_to_elt16(void* out, const float* in, int R, int V, int ld_out, bool f16, cudaStream_t st);
+int elt16_to_f32(float* out, const void* in_bf16, int64_t n, cudaStream_t st);
 
 // Paged attention with a per-head linear distance bias and an optional chunk mask.
 //   score(i, j) = scale * q_i . k_j - slope_h * (i - j),  slope_h = 2^(-bias_span * (h + 1) / H)   (bias_span = 0: no bias)

@@ -131,7 +131,7 @@ int embed_f32(float* res, const int32_t* ids, const void* table, int T, int d, i
 }
 
 template <typename E>
-__global__ void rmsnorm_f32in_kernel(E* y, const float* x, const int32_t* rows, const E* w, int d, float eps, float offset) {
+__global__ void rmsnorm_f32in_kernel(E* y, const float* x, const int32_t* rows, const E* w, int d, float eps, float offset, float out_scale) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[33];
@@ -140,14 +140,15 @@ __global__ void rmsnorm_f32in_kernel(E* y, const float* x, const int32_t* rows, 
   float ss = 0.f;
   for (int c = threadIdx.x; c < d; c += blockDim.x) { const float v = src[c]; ss = fmaf(v, v, ss); }
   ss = block_sum(ss, red);
-  const float inv = 1.f / sqrtf(ss / (float)d + eps);
+  const float inv = out_scale / sqrtf(ss / (float)d + eps);
   for (int c = threadIdx.x; c < d; c += blockDim.x) stf(y + (int64_t)r * d + c, src[c] * inv * (offset + ldf(w + c)));
 }
-int rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, int elt, cudaStream_t st) {
+int rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, float out_scale, int elt,
+                  cudaStream_t st) {
   if (R <= 0) return 0;
   cudaError_t ce = elt == KGE_ELT_F32
-      ? launch_pdl(rmsnorm_f32in_kernel<float>, dim3(R), dim3(256), 0, st, (float*)y, x, rows, (const float*)w, d, eps, offset)
-      : launch_pdl(rmsnorm_f32in_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, st, (__nv_bfloat16*)y, x, rows, (const __nv_bfloat16*)w, d, eps, offset);
+      ? launch_pdl(rmsnorm_f32in_kernel<float>, dim3(R), dim3(256), 0, st, (float*)y, x, rows, (const float*)w, d, eps, offset, out_scale)
+      : launch_pdl(rmsnorm_f32in_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, st, (__nv_bfloat16*)y, x, rows, (const __nv_bfloat16*)w, d, eps, offset, out_scale);
   KGE_CUDA_OK(ce);
   return 0;
 }
@@ -186,6 +187,17 @@ int logits_to_elt16(void* out, const float* in, int R, int V, int ld_out, bool f
   if (R <= 0) return 0;
   const int grid = (int)std::min<int64_t>(((int64_t)R * V + 255) / 256, 148 * 8);
   KGE_CUDA_OK(launch_pdl(logits_to_elt16_kernel, dim3(grid), dim3(256), 0, st, (uint16_t*)out, in, R, V, ld_out, f16));
+  return 0;
+}
+
+__global__ void elt16_to_f32_kernel(float* out, const __nv_bfloat16* in, int64_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) out[i] = __bfloat162float(in[i]);
+}
+int elt16_to_f32(float* out, const void* in_bf16, int64_t n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  KGE_CUDA_OK(launch_pdl(elt16_to_f32_kernel, dim3((unsigned)std::min<int64_t>((n + 255) / 256, 148 * 8)), dim3(256), 0, st, out, (const __nv_bfloat16*)in_bf16, n));
   return 0;
 }
 
