@@ -522,6 +522,99 @@ def run_ours(args):
 _REAL_STDOUT = None
 
 
+# ------------------------------------------------------------------------------------------------ design comparison
+DESIGN_SIZES = {
+    # layer-list model (Safupel) sizes that resemble real layers, and the Llama of about equal weight bytes beside them
+    "w2048": dict(width=2048, vocab=32000, reps=2, heads=16, kv=4, dim=128, chunk=1024, m_heads=4, m_dim=128, m_vdim=256,
+                  r_width=2560, r_blocks=16, conv=4, ff=8192, experts=16, top=2, eff=1024, sff=2048, llama_ffn=5632),
+    "w4096": dict(width=4096, vocab=32000, reps=1, heads=32, kv=8, dim=128, chunk=2048, m_heads=8, m_dim=128, m_vdim=256,
+                  r_width=4096, r_blocks=16, conv=4, ff=14336, experts=8, top=2, eff=3584, sff=3584, llama_ffn=11008),
+}
+
+
+def design_configs(z):
+    par = {"left": {"dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv"], "mask": {"size": z["chunk"]}, "scale": z["dim"] ** -0.5, "vdim": z["dim"]},
+           "left_scale": 1.0, "right": {"dim": z["m_dim"], "gate_cap": 15.0, "heads": z["m_heads"], "vdim": z["m_vdim"]}, "right_scale": 1.0}
+    rec = {"blocks": z["r_blocks"], "conv": z["conv"], "width": z["r_width"]}
+    dense = {"ff": z["ff"], "kind": "dense"}
+    moe = {"expert": {"ff": z["eff"]}, "kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["sff"]}}
+    four = [{"mixer": par, "mlp": dense, "type": "parallel"}, {"mixer": rec, "mlp": moe, "type": "rglru"},
+            {"mixer": rec, "mlp": dense, "type": "rglru"}, {"mixer": par, "mlp": moe, "type": "parallel"}]
+    hyb = {"architecture": "Safupel", "layers": four * z["reps"], "logit_scale": 1.0, "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": z["width"]}
+    lla = {"model_type": "llama", "vocab_size": z["vocab"], "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 8192,
+           "hidden_size": z["width"], "num_hidden_layers": 4 * z["reps"], "intermediate_size": z["llama_ffn"], "num_attention_heads": z["heads"],
+           "num_key_value_heads": z["kv"], "head_dim": z["dim"], "tie_word_embeddings": False, "bos_token_id": 1, "eos_token_id": 2}
+    return hyb, lla
+
+
+def time_raw_steps(kge, llm, batch_np, steps, warmup):
+    """Wall-clock seconds per synchronous engine step (metadata upload, kernels, sampled ids back), after warm-up."""
+    import ctypes as C
+    import numpy as np
+    keep = {k: np.ascontiguousarray(v) for k, v in batch_np.items()}
+    b = kge.StepBatch(len(keep["ids"]), len(keep["seq_lens"]), keep["ids"].ctypes.data, keep["pos"].ctypes.data, keep["qsl"].ctypes.data,
+                      keep["seq_lens"].ctypes.data, keep["btab"].ctypes.data, keep["btab"].shape[1], keep["slots"].ctypes.data,
+                      keep["rows"].ctypes.data, len(keep["rows"]), None)
+    out = np.zeros(len(keep["rows"]) + 1, dtype=np.int32)
+    for _ in range(warmup):
+        kge.check(kge.lib().kge_step(llm._h, C.byref(b), out.ctypes.data, None), "kge_step")
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        kge.check(kge.lib().kge_step(llm._h, C.byref(b), out.ctypes.data, None), "kge_step")
+    return (time.perf_counter() - t0) / steps
+
+
+def raw_batch(B, ctx, q, bs, vocab, seed):
+    """B requests that run their last q tokens at context ctx; request i owns blocks 1 + i * per .. of the pool."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    per = (ctx + bs - 1) // bs
+    ids = rng.integers(3, vocab - 1, size=B * q, dtype=np.int32)
+    pos = np.tile(np.arange(ctx - q, ctx, dtype=np.int32), B)
+    qsl = np.arange(0, B * q + 1, q, dtype=np.int32)
+    btab = (1 + np.arange(B * per, dtype=np.int32)).reshape(B, per)
+    slots = (btab[:, :, None].astype(np.int64) * bs + np.arange(bs)[None, None, :]).reshape(B, per * bs)[:, ctx - q:ctx].reshape(-1)
+    return dict(ids=ids, pos=pos, qsl=qsl, seq_lens=np.full(B, ctx, dtype=np.int32), btab=btab, slots=slots, rows=qsl[1:] - 1)
+
+
+def run_designs(args):
+    """--designs: the layer-list design next to a Llama of equal size (random weights): one prefill step of 4 x 2048 tokens,
+    one decode step of 64 requests at context 2048, wall-clock per step plus per-kernel device times against the roofline."""
+    from kge_loader import load
+    kge = load()
+    kge.require_cuda()
+    hbm, tf, src = peaks()
+    B, ctx, PB, bs = 64, 2048, 4, args.block_size
+    for name, z in DESIGN_SIZES.items():
+        line = {"design_compare": name, "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+                "prefill": f"{PB} x {ctx} tokens in one step", "decode": f"{B} requests, one token each at context {ctx}", "arms": {}}
+        for arm, cfg in zip(("safupel", "llama"), design_configs(z)):
+            with tempfile.TemporaryDirectory() as d:
+                json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+                llm = kge.LLM(d, load_format="dummy", seed=1, dtype="bfloat16", block_size=bs, max_model_len=ctx + 64, max_num_seqs=B,
+                              max_num_batched_tokens=PB * ctx, num_gpu_blocks_override=B * ((ctx + bs) // bs) + 2, enable_prefix_caching=False)
+            rec = {"weight_gb": llm.weight_bytes / 1e9}
+            pre = raw_batch(PB, ctx, ctx, bs, z["vocab"], 1)
+            dec = raw_batch(B, ctx, 1, bs, z["vocab"], 2)
+            for r0 in range(0, B, PB):           # fill every request's cache and state first
+                fill = raw_batch(B, ctx, ctx, bs, z["vocab"], 3)
+                sub = dict(ids=fill["ids"][r0 * ctx:(r0 + PB) * ctx], pos=fill["pos"][:PB * ctx], qsl=fill["qsl"][:PB + 1],
+                           seq_lens=fill["seq_lens"][:PB], btab=fill["btab"][r0:r0 + PB], slots=fill["slots"][r0 * ctx:(r0 + PB) * ctx], rows=fill["rows"][:PB])
+                time_raw_steps(kge, llm, sub, 1, 0)
+            for phase, batch, ntok in (("prefill", pre, PB * ctx), ("decode", dec, B)):
+                sec = time_raw_steps(kge, llm, batch, args.steps, max(3, args.warmup))
+                llm.set_timing(True)
+                time_raw_steps(kge, llm, batch, 1, 0)
+                stats = llm.kernel_stats()
+                llm.set_timing(False)
+                rec[phase] = {"ms_per_step": sec * 1e3, "tokens_per_s": ntok / sec, "kernels": {
+                    k: {"launches": v["launches"], "ms": round(v["ms"], 4), "hbm_frac": round(v["bytes"] / 1e9 / (v["ms"] / 1e3) / hbm, 3) if v["ms"] else None,
+                        "tensor_frac": round(v["flops"] / 1e12 / (v["ms"] / 1e3) / tf, 3) if v["ms"] else None} for k, v in stats.items()}}
+            llm.close()
+            line["arms"][arm] = rec
+        emit(line)
+
+
 def protect_stdout():
     """stdout carries exactly ONE JSON line: anything libraries print there (NCCL's version banner,
     torchrun notices) is sent to stderr instead; emit() writes to the saved descriptor."""
@@ -549,10 +642,14 @@ def main():
     ap.add_argument("--no-tp", action="store_true", help="at N > 1, skip the tensor-parallel (config 4) sub-record")
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"], help="TP data path: peer memory (default) or NCCL")
     ap.add_argument("--tp-timeout", type=float, default=420.0, help="seconds the tensor-parallel leg may take at N > 1")
+    ap.add_argument("--designs", action="store_true", help="instead of the workload: the layer-list design (Safupel) beside a Llama of equal "
+                    "size, prefill and decode steps with per-kernel rooflines (one GPU, random weights)")
     args = ap.parse_args()
     args.warmup_ref = args.warmup        # same warm-up count as the GPU arm
     protect_stdout()
-    if args.impl == "reference":
+    if args.designs:
+        run_designs(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

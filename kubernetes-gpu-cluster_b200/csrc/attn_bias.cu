@@ -73,8 +73,225 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_bias_chunk_kernel(AttnBia
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// bfloat16, head sizes that are multiples of 16 (keys) / 8 (values) up to 128: the same attention on the tensor cores
+// (mma.sync m16n8k16).  A CTA owns 16 rows - consecutive (token, query head of one key/value head) pairs of one
+// request, so neighbouring tokens and the heads of a group share every key tile - and its four warps take the 32-key
+// tiles of the rows' chunk in turn: K and V of a tile are staged in the warp's own shared memory with 16-byte loads,
+// S = Q K^T and O += P V are mma instructions with fp32 accumulators, bias, mask and softmax statistics stay in fp32,
+// and the four partial results (m, l, O) are merged through shared memory at the end.  Decoding a single token is the
+// same kernel with hpg rows in use: its four warps split the chunk's keys.
+constexpr int AM_WARPS = 4, AM_KT = 32, AM_MAXD = 128, AM_PAD = 8;
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+__device__ __forceinline__ uint32_t pack2raw(__nv_bfloat16 lo, __nv_bfloat16 hi) {
+  return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+}
+
+__global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  typedef __nv_bfloat16 E;
+  extern __shared__ __align__(16) unsigned char am_smem[];
+  const int b = blockIdx.z, g = blockIdx.y, hpg = a.H / a.G;
+  const int rs = a.qsl[b], nrows = (a.qsl[b + 1] - rs) * hpg, R0 = blockIdx.x * 16;
+  if (R0 >= nrows) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, qr = lane >> 2, qc = (lane & 3) * 2;
+  const int dim = a.dim, vdim = a.vdim, ksteps = dim >> 4, vtiles = vdim >> 3;
+  const int kst = dim + AM_PAD, vst = vdim + AM_PAD;                 // shared row strides (elements)
+  const size_t region = (size_t)AM_KT * (kst + vst) * sizeof(E);
+  E* Ks = reinterpret_cast<E*>(am_smem + warp * region);
+  E* Vs = Ks + AM_KT * kst;
+  // this thread's two rows: qr and qr + 8 of the tile
+  int pos[2], lo[2], tok[2], head[2];
+  float slope2[2];
+  const float log2e = 1.4426950408889634f;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = R0 + qr + 8 * h;
+    const bool valid = r < nrows;
+    tok[h] = rs + (valid ? r : nrows - 1) / hpg;
+    head[h] = g * hpg + (valid ? r : nrows - 1) % hpg;
+    pos[h] = valid ? a.positions[tok[h]] : -1;                       // -1: no key is visible, the row is never written
+    lo[h] = (a.chunk > 0 && pos[h] >= 0) ? (pos[h] / a.chunk) * a.chunk : 0;
+    slope2[h] = a.bias_span > 0.f ? exp2f(-a.bias_span * (float)(head[h] + 1) / (float)a.H) * log2e : 0.f;
+  }
+  const int pos_first = a.positions[rs + R0 / hpg], pos_last = a.positions[rs + min(R0 + 15, nrows - 1) / hpg];
+  const int lo_min = a.chunk > 0 ? (pos_first / a.chunk) * a.chunk : 0;
+  const int ntiles = (pos_last - lo_min + AM_KT) / AM_KT;
+  const float scale2 = a.scale * log2e;
+  uint32_t qf[AM_MAXD / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < AM_MAXD / 16; ++ks) {
+    if (ks < ksteps) {
+      const E* q0 = (const E*)a.q + (int64_t)tok[0] * a.ldq + head[0] * dim + ks * 16 + qc;
+      const E* q1 = (const E*)a.q + (int64_t)tok[1] * a.ldq + head[1] * dim + ks * 16 + qc;
+      qf[ks][0] = pos[0] >= 0 ? *reinterpret_cast<const uint32_t*>(q0) : 0u;
+      qf[ks][1] = pos[1] >= 0 ? *reinterpret_cast<const uint32_t*>(q1) : 0u;
+      qf[ks][2] = pos[0] >= 0 ? *reinterpret_cast<const uint32_t*>(q0 + 8) : 0u;
+      qf[ks][3] = pos[1] >= 0 ? *reinterpret_cast<const uint32_t*>(q1 + 8) : 0u;
+    } else {
+      qf[ks][0] = qf[ks][1] = qf[ks][2] = qf[ks][3] = 0u;
+    }
+  }
+  float o[AM_MAXD / 8][4];
+#pragma unroll
+  for (int v = 0; v < AM_MAXD / 8; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int32_t* bt = a.block_table + (int64_t)b * a.max_blocks;
+  const E* kc = (const E*)a.k_cache;
+  const E* vc = (const E*)a.v_cache;
+  const int kseg = dim >> 3, vseg = vdim >> 3;
+  for (int kt = warp; kt < ntiles; kt += AM_WARPS) {
+    const int j0 = lo_min + kt * AM_KT;
+    // stage the tile: lane i knows where key j0 + i lives; the 16-byte pieces of a row are fetched by consecutive lanes
+    const int jl = j0 + lane;
+    const int64_t myrow = jl <= pos_last ? ((int64_t)bt[jl / a.block_size] * a.G + g) * a.block_size + jl % a.block_size : -1;
+    for (int idx = lane; idx < AM_KT * kseg; idx += 32) {
+      const int key = idx / kseg, seg = idx % kseg;
+      const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row >= 0) v = *reinterpret_cast<const uint4*>(kc + row * dim + seg * 8);
+      *reinterpret_cast<uint4*>(Ks + key * kst + seg * 8) = v;
+    }
+    for (int idx = lane; idx < AM_KT * vseg; idx += 32) {
+      const int key = idx / vseg, seg = idx % vseg;
+      const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row >= 0) v = *reinterpret_cast<const uint4*>(vc + row * vdim + seg * 8);
+      *reinterpret_cast<uint4*>(Vs + key * vst + seg * 8) = v;
+    }
+    __syncwarp();
+    float sacc[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < AM_MAXD / 16; ++ks) {
+      if (ks < ksteps) {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const E* kp = Ks + (nt * 8 + qr) * kst + ks * 16 + qc;
+          mma_16816(sacc[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+        }
+      }
+    }
+    // bias, mask, running maximum (exponent base 2)
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int h = c >> 1, j = j0 + nt * 8 + qc + (c & 1);
+        const bool vis = j <= pos[h] && j >= lo[h];
+        const float sv = vis ? sacc[nt][c] * scale2 - slope2[h] * (float)(pos[h] - j) : -INFINITY;
+        sacc[nt][c] = sv;
+        tmax[h] = fmaxf(tmax[h], sv);
+      }
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
+      tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
+      const float mn = fmaxf(m[h], tmax[h]);
+      corr[h] = mn == -INFINITY ? 1.f : exp2f(m[h] - mn);
+      m[h] = mn;
+      l[h] *= corr[h];
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int h = c >> 1;
+        const float p = sacc[nt][c] == -INFINITY ? 0.f : exp2f(sacc[nt][c] - m[h]);
+        sacc[nt][c] = p;
+        l[h] += p;
+      }
+#pragma unroll
+    for (int v = 0; v < AM_MAXD / 8; ++v) { o[v][0] *= corr[0]; o[v][1] *= corr[0]; o[v][2] *= corr[1]; o[v][3] *= corr[1]; }
+    uint32_t pf[2][4];
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      pf[kk][0] = pack2(sacc[2 * kk][0], sacc[2 * kk][1]);
+      pf[kk][1] = pack2(sacc[2 * kk][2], sacc[2 * kk][3]);
+      pf[kk][2] = pack2(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+      pf[kk][3] = pack2(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+    }
+#pragma unroll
+    for (int v = 0; v < AM_MAXD / 8; ++v) {
+      if (v < vtiles) {
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const E* vp = Vs + (kk * 16 + qc) * vst + v * 8 + qr;
+          mma_16816(o[v], pf[kk], pack2raw(vp[0], vp[vst]), pack2raw(vp[8 * vst], vp[9 * vst]));
+        }
+      }
+    }
+    __syncwarp();
+  }
+  // merge the four warps' partial results
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  __syncthreads();                                          // every warp is done with its tiles: the regions are free
+  float* Os = reinterpret_cast<float*>(am_smem + warp * region);      // [16][vdim]
+  float* ML = reinterpret_cast<float*>(am_smem + AM_WARPS * region);  // [warps][2][16]
+#pragma unroll
+  for (int v = 0; v < AM_MAXD / 8; ++v) {
+    if (v < vtiles) {
+      Os[qr * vdim + v * 8 + qc] = o[v][0]; Os[qr * vdim + v * 8 + qc + 1] = o[v][1];
+      Os[(qr + 8) * vdim + v * 8 + qc] = o[v][2]; Os[(qr + 8) * vdim + v * 8 + qc + 1] = o[v][3];
+    }
+  }
+  if ((lane & 3) == 0) {
+    ML[(warp * 2 + 0) * 16 + qr] = m[0]; ML[(warp * 2 + 0) * 16 + qr + 8] = m[1];
+    ML[(warp * 2 + 1) * 16 + qr] = l[0]; ML[(warp * 2 + 1) * 16 + qr + 8] = l[1];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < 16 * vdim; idx += AM_WARPS * 32) {
+    const int r = idx / vdim, c = idx % vdim;
+    if (R0 + r >= nrows) continue;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < AM_WARPS; ++w) M = fmaxf(M, ML[(w * 2) * 16 + r]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < AM_WARPS; ++w) {
+      const float mw = ML[(w * 2) * 16 + r];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      num = fmaf(f, reinterpret_cast<const float*>(am_smem + w * region)[r * vdim + c], num);
+      den = fmaf(f, ML[(w * 2 + 1) * 16 + r], den);
+    }
+    const int row = R0 + r;
+    E* out = (E*)a.out + (int64_t)(rs + row / hpg) * a.ldo + (g * hpg + row % hpg) * vdim + c;
+    *out = __float2bfloat16_rn(num / den * a.out_scale);
+  }
+}
+
 int attn_bias_chunk(const AttnBiasArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
+  if (a.elt == KGE_ELT_BF16 && a.max_q > 0 && a.dim % 16 == 0 && a.dim <= AM_MAXD && a.vdim % 8 == 0 && a.vdim <= AM_MAXD && a.ldq % 2 == 0 &&
+      a.H % a.G == 0 && (reinterpret_cast<uintptr_t>(a.q) & 3) == 0 && a.B <= 65535 && a.G <= 65535) {
+    const int hpg = a.H / a.G;
+    const size_t smem = (size_t)AM_WARPS * AM_KT * (a.dim + a.vdim + 2 * AM_PAD) * 2 + (size_t)AM_WARPS * 2 * 16 * 4;
+    static size_t smem_set = 0;                       // opt in once per size that needs more than the default 48 KB
+    if (smem > 48 * 1024 && smem > smem_set) {
+      KGE_CUDA_OK(cudaFuncSetAttribute(attn_bias_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      smem_set = smem;
+    }
+    const dim3 grid((a.max_q * hpg + 15) / 16, a.G, a.B);
+    KGE_CUDA_OK(launch_pdl(attn_bias_mma_kernel, grid, dim3(AM_WARPS * 32), smem, st, a));
+    return 0;
+  }
   KGE_REQUIRE(a.vdim <= 32 * ATT_MAXV, "attn_bias_chunk: value head size %d > %d", a.vdim, 32 * ATT_MAXV);
   KGE_REQUIRE(a.dim <= 1024 && a.H % a.G == 0, "attn_bias_chunk: bad head sizes");
   const int64_t items = (int64_t)a.T * a.H;

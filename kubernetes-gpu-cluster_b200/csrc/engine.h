@@ -89,7 +89,7 @@ struct kge_engine {
   bool f32 = false;                          // float32 storage and arithmetic (--dtype float32; layer-list models only)
   // layer-list ("hybrid") models: fp32 residual stream, their own activation arena and the recurrent-state pool
   std::vector<kge::HybridLayerW> hyb;
-  float *res32 = nullptr, *gates32 = nullptr, *logits32 = nullptr, *state = nullptr;
+  float *res32 = nullptr, *gates32 = nullptr, *logits32 = nullptr, *state = nullptr, *mo32 = nullptr;
   void *hx = nullptr, *pbuf = nullptr, *ubuf = nullptr, *mixbuf = nullptr, *obuf1 = nullptr, *obuf2 = nullptr, *ffbuf = nullptr;
   void *moe_hidden = nullptr, *moe_out = nullptr, *hsel = nullptr;
   int32_t *moe_goff = nullptr, *moe_ptok = nullptr, *moe_pdest = nullptr, *moe_cexp = nullptr;

@@ -43,6 +43,7 @@ struct ResidentStep {
 extern "C" int kge_engine_run_resident(kge_engine* e, const int32_t* prompts_host, int32_t B, int32_t prompt_len,
                                        int32_t out_len, int32_t prefill_batch, int32_t* out_tokens_host, float* ms,
                                        float* decode_ms) {
+  KGE_REQUIRE(e && !e->spec.is_hybrid(), "kge_engine_run_resident: not available for layer-list models (their steps also carry state slots)");
   KGE_REQUIRE(e && prompts_host && out_tokens_host && ms, "kge_engine_run_resident: null argument");
   KGE_REQUIRE(B > 0 && prompt_len > 0 && out_len > 0 && prefill_batch > 0, "kge_engine_run_resident: bad sizes");
   KGE_REQUIRE(!e->sched->has_unfinished(), "kge_engine_run_resident: the scheduler must be idle");
@@ -198,6 +199,7 @@ extern "C" int kge_engine_record_steps(kge_engine* e, int enable) {
 
 extern "C" int kge_engine_replay_recorded(kge_engine* e, int32_t* out_tokens_host, int64_t* out_request_ids_host, int64_t cap,
                                           int64_t* n_samples, int32_t* n_steps, float* ms, float* decode_ms) {
+  KGE_REQUIRE(e && !e->spec.is_hybrid(), "kge_engine_replay_recorded: not available for layer-list models (their steps also carry state slots)");
   KGE_REQUIRE(e && out_tokens_host && out_request_ids_host && n_samples && ms, "kge_engine_replay_recorded: null argument");
   KGE_REQUIRE(!e->recording && !e->recorded.empty(), "kge_engine_replay_recorded: record a job first (kge_engine_record_steps)");
   KGE_REQUIRE(!e->sched->has_unfinished(), "kge_engine_replay_recorded: the scheduler must be idle");

@@ -188,9 +188,14 @@ int engine_forward(kge_engine* e, int T, int B, int R, int max_blocks, int max_q
 
 int engine_decode_step(kge_engine* e, int B, int stride, int max_seq_len, const StepMeta& dm, bool any_random, double sum_seq) {
   const double attn_flops = 4.0 * sum_seq;
-  const int ns = attn_decode_splits(B, e->KV_loc, max_seq_len);
-  if (!e->use_graphs || e->timing || e->step_num_masks > 0)      // a masked step is rare and its mask list is not part of a graph
-    return engine_forward(e, B, B, B, stride, 1, max_seq_len, dm, any_random, sum_seq, attn_flops);
+  const bool hybrid = e->spec.is_hybrid();
+  const int ns = hybrid ? 0 : attn_decode_splits(B, e->KV_loc, max_seq_len);
+  auto forward = [&]() -> int {
+    return hybrid ? hybrid_forward(e, B, B, B, stride, dm, any_random)
+                  : engine_forward(e, B, B, B, stride, 1, max_seq_len, dm, any_random, sum_seq, attn_flops);
+  };
+  if (!e->use_graphs || e->timing || e->step_num_masks > 0 || e->layer_dump_host)      // a masked step is rare and its mask list is not part of a graph
+    return forward();
   for (auto& g : e->graphs)
     if (g.B == B && g.ns == ns && g.stride == stride && g.rnd == any_random) {
       KGE_CUDA_OK(cudaGraphLaunch(g.exec, e->stream));
@@ -202,10 +207,10 @@ int engine_decode_step(kge_engine* e, int B, int stride, int max_seq_len, const 
   for (auto& kv : e->graph_seen) if (kv.first == key) seen = &kv.second;
   if (!seen) { e->graph_seen.push_back({key, 0}); seen = &e->graph_seen.back().second; }
   if ((*seen)++ == 0)     // first sight: run eagerly so every lazy initialisation happens outside a capture
-    return engine_forward(e, B, B, B, stride, 1, max_seq_len, dm, any_random, sum_seq, attn_flops);
+    return forward();
   const int64_t l0 = e->launches;
   KGE_CUDA_OK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
-  const int rc = engine_forward(e, B, B, B, stride, 1, max_seq_len, dm, any_random, sum_seq, attn_flops);
+  const int rc = forward();
   cudaGraph_t graph = nullptr;
   cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
   if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
@@ -316,11 +321,11 @@ static int run_step(kge_engine* e, const kge_step_batch* b, const float* temp, c
   KGE_CUDA_OK(cudaMemcpyAsync(e->meta_dev, e->meta_host, (size_t)bytes, cudaMemcpyHostToDevice, e->stream));
   e->h2d_bytes += bytes;
   e->d2h_bytes += (int64_t)R * 4;
-  if (hybrid) {
-    e->want_logits32 = out_logits_host != nullptr;
-    if (int rc = hybrid_forward(e, T, B, R, stride, dm, any_random)) return rc;
-  } else if (decode_only && max_q == 1) {
+  e->want_logits32 = out_logits_host != nullptr;
+  if (decode_only && max_q == 1) {
     if (int rc = engine_decode_step(e, B, stride, max_seq, dm, any_random, sum_seq)) return rc;
+  } else if (hybrid) {
+    if (int rc = hybrid_forward(e, T, B, R, stride, dm, any_random)) return rc;
   } else {
     if (int rc = engine_forward(e, T, B, R, stride, max_q, max_seq, dm, any_random, sum_seq, attn_flops)) return rc;
   }

@@ -105,6 +105,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   HB_OK(e->final_w = (bf16*)b.mat({"final.norm"}, {d}, 1, 0.f, 0.f));
   e->hyb.resize(s.L);
   int64_t state_floats = 0;
+  int max_mo = 1;
   int max_proj = 1, max_mix = 1, max_ff = 1, max_gate = 1, max_u = 1, max_top = 0, max_eff = 1, max_E = 1;
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
@@ -153,6 +154,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
         HB_OK(L.o2.w = b.upload(cat));
       }
       state_floats += mlstm_state_floats(h.m_heads, h.m_dim, h.m_vdim);
+      max_mo = std::max(max_mo, mv);
       max_proj = std::max(max_proj, L.proj.N); max_mix = std::max(max_mix, ko); max_gate = std::max(max_gate, 2 * h.m_heads);
     }
     if (h.mlp == HybridLayerSpec::DENSE) {
@@ -199,6 +201,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   e->obuf2 = aalloc((int64_t)Tm * d, es);
   e->ffbuf = aalloc((int64_t)Tm * max_ff, es);
   e->gates32 = (float*)aalloc((int64_t)Tm * max_gate, 4);
+  e->mo32 = (float*)aalloc((int64_t)Tm * max_mo, 4);
   e->hsel = aalloc((int64_t)std::max(Rm, Tm) * d, es);
   // logits rows: the sampled rows of a step, or every row a trace asks for
   e->logits32 = (float*)aalloc((int64_t)std::max(Rm, Tm) * s.vocab, 4);
@@ -221,7 +224,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   e->max_blocks_per_seq = (e->cfg.max_model_len + e->cfg.block_size - 1) / e->cfg.block_size;
   carve_meta(nullptr, Tm, Rm, std::max(Rm, Tm), e->max_blocks_per_seq, &e->meta_bytes);
   e->meta_dev = (uint8_t*)aalloc(e->meta_bytes, 1);
-  if (!e->res32 || !e->hx || !e->pbuf || !e->ubuf || !e->mixbuf || !e->obuf1 || !e->obuf2 || !e->ffbuf || !e->gates32 || !e->hsel ||
+  if (!e->res32 || !e->hx || !e->pbuf || !e->ubuf || !e->mixbuf || !e->obuf1 || !e->obuf2 || !e->ffbuf || !e->gates32 || !e->mo32 || !e->hsel ||
       !e->logits32 || !e->logits || !e->state || !e->d_out || !e->lp_vals || !e->lp_ids || !e->lp_rank || !e->mask_pairs || !e->meta_dev)
     return fail("activation arena allocation failed: " + b.err);
   if (cudaMallocHost((void**)&e->meta_host, e->meta_bytes) != cudaSuccess ||
@@ -274,7 +277,6 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   sc.eos_token_id = s.eos;
   sc.num_state_slots = e->cfg.max_num_seqs;        // every running request owns a slot of the recurrent-state pool
   e->sched.reset(new Scheduler(sc));
-  e->use_graphs = false;
   if (cudaStreamSynchronize(e->stream) != cudaSuccess) return fail(std::string("device error during initialisation: ") + cudaGetErrorString(cudaGetLastError()));
   return 0;
 }
@@ -364,13 +366,14 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       aa.block_table = m.btab; aa.max_blocks = max_blocks; aa.seq_lens = m.seq_lens; aa.qsl = m.qsl; aa.positions = m.pos; aa.token_req = m.treq;
       aa.B = B; aa.T = T; aa.H = h.heads; aa.G = h.kv_heads; aa.dim = h.dim; aa.vdim = h.vdim; aa.block_size = bs; aa.chunk = h.chunk;
       aa.scale = h.scale; aa.bias_span = 8.f; aa.out_scale = h.left_scale; aa.elt = elt;
+      for (int r = 0; r < B; ++r) aa.max_q = std::max(aa.max_q, hm.qsl[r + 1] - hm.qsl[r]);
       double keys = 0;                                   // visible keys over all rows
       for (int t = 0; t < T; ++t) keys += h.chunk > 0 ? hm.pos[t] % h.chunk + 1 : hm.pos[t] + 1;
       HFWD(decode_only ? C_ATT_DEC : C_ATT_GEN, (decode_only ? keys : (double)T) * h.kv_heads * (h.dim + h.vdim) * es + (double)T * h.heads * (h.dim + h.vdim) * es,
            2.0 * keys * h.heads * (h.dim + h.vdim), attn_bias_chunk(aa, st));
       MlstmArgs ma;
       ma.q = at(e->pbuf, L.off_mq); ma.k = at(e->pbuf, L.off_mk); ma.v = at(e->pbuf, L.off_mv); ma.g = at(e->pbuf, L.off_mg); ma.ld = ldp;
-      ma.gates = e->gates32; ma.norm_w = L.m_norm; ma.out = at(e->mixbuf, ka); ma.ldo = ko;
+      ma.gates = e->gates32; ma.o_scratch = e->mo32; ma.norm_w = L.m_norm; ma.out = at(e->mixbuf, ka); ma.ldo = ko;
       ma.state = e->state + L.state_off; ma.slot_stride = e->slot_stride; ma.slots = m.sslot; ma.qsl = m.qsl; ma.positions = m.pos;
       ma.B = B; ma.T = T; ma.H = h.m_heads; ma.dim = h.m_dim; ma.vdim = h.m_vdim;
       ma.cap = h.gate_cap; ma.q_scale = 1.f / sqrtf((float)h.m_dim); ma.eps = s.eps; ma.den_eps = 1e-6f; ma.out_scale = h.right_scale; ma.elt = elt;

@@ -61,6 +61,7 @@ struct AttnBiasArgs {
   const int32_t* seq_lens = nullptr; const int32_t* qsl = nullptr; const int32_t* positions = nullptr;
   const int32_t* token_req = nullptr;      // [T] request index of every token row
   int B = 0, T = 0, H = 0, G = 0, dim = 0, vdim = 0, block_size = 0, chunk = 0;
+  int max_q = 0;                           // the longest request's rows in this step (0 = unknown: the per-row kernel runs)
   float scale = 1.f, bias_span = 0.f, out_scale = 1.f;
   int elt = KGE_ELT_BF16;
 };
@@ -100,6 +101,8 @@ struct MlstmArgs {
   const void* q = nullptr; const void* k = nullptr; const void* v = nullptr; const void* g = nullptr; int ld = 0;   // one packed buffer
   const float* gates = nullptr;
   const void* norm_w = nullptr; void* out = nullptr; int ldo = 0;
+  float* o_scratch = nullptr;              // fp32 [T, H * vdim]: with it (and dim <= 128) the value columns of a head are split
+                                           // over several blocks with the state in registers, and a second kernel normalises
   float* state = nullptr; int64_t slot_stride = 0;
   const int32_t* slots = nullptr; const int32_t* qsl = nullptr; const int32_t* positions = nullptr;
   int B = 0, T = 0, H = 0, dim = 0, vdim = 0;

@@ -1,8 +1,9 @@
 // Shape-agnostic linear layer for layer-list models: any T / N / K and alignment, bfloat16 or float32 storage, fp32
-// accumulation in ascending k (so a row's result does not depend on what else is in the launch), optional row gather /
-// scatter, per-row input scale, grouped rows (one weight slice per group: mixture-of-experts) or strided slices
+// accumulation in a fixed k order (so a row's result does not depend on what else is in the launch), optional row
+// gather / scatter, per-row input scale, grouped rows (one weight slice per group: mixture-of-experts) or strided slices
 // (block-diagonal projections), gated pairs (silu(x.w) * (x.w2)) and fp32 output or accumulation.  Tiles of 64 x 64
-// outputs, 256 threads with 4 x 4 outputs each, operands staged in shared memory as fp32.
+// outputs and 256 threads: float32 storage multiplies on the fp32 pipes (4 x 4 outputs per thread, operands staged in
+// shared memory as fp32, true 32-bit products), bfloat16 storage on the tensor cores (mma.sync, further down).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -97,6 +98,110 @@ __global__ void __launch_bounds__(256) linear_any_kernel(LinearArgs a) {
   }
 }
 
+// bfloat16 operands: the same tiling on the tensor cores (mma.sync m16n8k16, fp32 accumulators).  Both operands are
+// k-contiguous, which is exactly the row x col fragment layout, so the fragments are 32-bit loads from k-padded shared
+// tiles.  Eight warps as 2 x 4, each 32 rows x 16 outputs; a row's sum is formed in the same k order whatever the launch holds.
+constexpr int MBK = 32, MPAD = 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// eight consecutive k of one row into a shared tile, zero beyond K or for a missing row; 16-byte load when aligned
+__device__ __forceinline__ void stage8(__nv_bfloat16* dst, const __nv_bfloat16* row, int k, int K, bool vec) {
+  if (row && vec && k + 8 <= K) { *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(row + k); return; }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i] = (row && k + i < K) ? row[k + i] : __float2bfloat16_rn(0.f);
+}
+
+template <typename O, bool DUAL>
+__global__ void __launch_bounds__(256) linear_mma_kernel(LinearArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  typedef __nv_bfloat16 E;
+  const int z = blockIdx.z;
+  int r0 = 0, r1 = a.T;
+  if (a.group_off) { r0 = a.group_off[z]; r1 = a.group_off[z + 1]; }
+  const int m0 = r0 + blockIdx.y * LBM;
+  if (m0 >= r1) return;
+  const int n0 = blockIdx.x * LBN;
+  const E* x = (const E*)a.x + z * a.x_zs;
+  const E* w = (const E*)a.w + z * a.w_zs;
+  const E* w2 = DUAL ? (const E*)a.w2 + z * a.w_zs : nullptr;
+  const E* bias = a.bias ? (const E*)a.bias + z * a.b_zs : nullptr;
+  O* y = (O*)a.y + z * a.y_zs;
+  __shared__ __align__(16) E xs[LBM][MBK + MPAD], ws[LBN][MBK + MPAD], ws2[DUAL ? LBN : 1][MBK + MPAD];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = (warp >> 2) * 32, wn = (warp & 3) * 16;
+  // staging: thread -> (row tid / 4, eight k at (tid % 4) * 8)
+  const int sr = tid >> 2, sk = (tid & 3) * 8;
+  const int gr = m0 + sr;
+  const E* xrow = gr < r1 ? x + (int64_t)(a.xrows ? a.xrows[gr] : gr) * a.ldx : nullptr;
+  const E* wrow = n0 + sr < a.N ? w + (int64_t)(n0 + sr) * a.K : nullptr;
+  const E* w2row = (DUAL && n0 + sr < a.N) ? w2 + (int64_t)(n0 + sr) * a.K : nullptr;
+  const bool xvec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && a.ldx % 8 == 0;
+  const bool wvec = ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && a.K % 8 == 0 && (!DUAL || (reinterpret_cast<uintptr_t>(w2) & 15) == 0);
+  float acc[2][2][4] = {}, acc2[DUAL ? 2 : 1][2][4] = {};
+  for (int k0 = 0; k0 < a.K; k0 += MBK) {
+    stage8(&xs[sr][sk], xrow, k0 + sk, a.K, xvec);
+    stage8(&ws[sr][sk], wrow, k0 + sk, a.K, wvec);
+    if (DUAL) stage8(&ws2[sr][sk], w2row, k0 + sk, a.K, wvec);
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < MBK / 16; ++ks) {
+      const int kc = ks * 16 + (lane & 3) * 2;
+      uint32_t af[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = wm + i * 16 + (lane >> 2);
+        af[i][0] = *reinterpret_cast<const uint32_t*>(&xs[r][kc]);
+        af[i][1] = *reinterpret_cast<const uint32_t*>(&xs[r + 8][kc]);
+        af[i][2] = *reinterpret_cast<const uint32_t*>(&xs[r][kc + 8]);
+        af[i][3] = *reinterpret_cast<const uint32_t*>(&xs[r + 8][kc + 8]);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = wn + j * 8 + (lane >> 2);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&ws[n][kc]), b1 = *reinterpret_cast<const uint32_t*>(&ws[n][kc + 8]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) mma_bf16_16816(acc[i][j], af[i], b0, b1);
+        if (DUAL) {
+          const uint32_t c0 = *reinterpret_cast<const uint32_t*>(&ws2[n][kc]), c1 = *reinterpret_cast<const uint32_t*>(&ws2[n][kc + 8]);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) mma_bf16_16816(acc2[i][j], af[i], c0, c1);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = m0 + wm + i * 16 + (lane >> 2) + hh * 8;
+      if (r >= r1) continue;
+      const float sc = a.row_scale ? a.row_scale[r] : 1.f;
+      const int yr = a.yrows ? a.yrows[r] : r;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int n = n0 + wn + j * 8 + (lane & 3) * 2 + c;
+          if (n >= a.N) continue;
+          const float s1 = acc[i][j][hh * 2 + c];
+          float v;
+          if (DUAL) v = act_apply(ACT_SILU, sc * s1) * (sc * acc2[i][j][hh * 2 + c]);
+          else v = act_apply(a.act, sc * s1 + (bias ? ldf(bias + n) : 0.f));
+          v *= a.alpha;
+          O* dst = y + (int64_t)yr * a.ldy + n;
+          if (a.accumulate) v += ldf(dst);
+          stf(dst, v);
+        }
+    }
+}
+
 int linear_any(const LinearArgs& a, cudaStream_t st) {
   KGE_REQUIRE(a.x && a.w && a.y && a.N > 0 && a.K > 0 && a.nz > 0, "linear_any: bad arguments");
   if (a.T <= 0) return 0;
@@ -107,8 +212,8 @@ int linear_any(const LinearArgs& a, cudaStream_t st) {
   const bool f32 = a.elt == KGE_ELT_F32;
   KGE_REQUIRE(!f32 || a.out_f32, "linear_any: float32 storage writes float32");
   if (f32) ce = a.w2 ? launch_pdl(linear_any_kernel<float, float, true>, grid, block, 0, st, a) : launch_pdl(linear_any_kernel<float, float, false>, grid, block, 0, st, a);
-  else if (a.out_f32) ce = a.w2 ? launch_pdl(linear_any_kernel<__nv_bfloat16, float, true>, grid, block, 0, st, a) : launch_pdl(linear_any_kernel<__nv_bfloat16, float, false>, grid, block, 0, st, a);
-  else ce = a.w2 ? launch_pdl(linear_any_kernel<__nv_bfloat16, __nv_bfloat16, true>, grid, block, 0, st, a) : launch_pdl(linear_any_kernel<__nv_bfloat16, __nv_bfloat16, false>, grid, block, 0, st, a);
+  else if (a.out_f32) ce = a.w2 ? launch_pdl(linear_mma_kernel<float, true>, grid, block, 0, st, a) : launch_pdl(linear_mma_kernel<float, false>, grid, block, 0, st, a);
+  else ce = a.w2 ? launch_pdl(linear_mma_kernel<__nv_bfloat16, true>, grid, block, 0, st, a) : launch_pdl(linear_mma_kernel<__nv_bfloat16, false>, grid, block, 0, st, a);
   KGE_CUDA_OK(ce);
   return 0;
 }

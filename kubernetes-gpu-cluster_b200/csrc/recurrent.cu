@@ -166,8 +166,111 @@ __global__ void mlstm_step_kernel(MlstmArgs a) {
   if (tid == 0) slot[(int64_t)dim * vdim + dim] = m;
 }
 
+// The same recurrence with a head's value columns split over blocks of 64 threads: a thread keeps its column of the
+// state in registers (dim <= 128), the first warp keeps the normaliser n, and the un-normalised read-out goes to an fp32
+// scratch; mlstm_norm_gate_kernel then divides each head by its root mean square and applies weight and output gate.
+// More blocks than (request, head) pairs fill the machine when few requests prefill, and the state never sits in shared memory.
+constexpr int ML_MAXD = 128, ML_COLS = 64;
+
+template <typename E>
+__global__ void __launch_bounds__(ML_COLS) mlstm_cols_kernel(MlstmArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ __align__(16) float ks[ML_MAXD], qs[ML_MAXD], nv[ML_MAXD];
+  __shared__ float nq_s;
+  const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, c = blockIdx.z * ML_COLS + tid;
+  const int dim = a.dim, vdim = a.vdim;
+  const bool col = c < vdim;
+  const int rs = a.qsl[b], re = a.qsl[b + 1], p0 = a.positions[rs];
+  float* slot = a.state + (int64_t)a.slots[b] * a.slot_stride + (int64_t)h * ((int64_t)dim * vdim + dim + 1);
+  const bool fresh = p0 == 0;
+  float S[ML_MAXD];
+#pragma unroll
+  for (int d = 0; d < ML_MAXD; ++d) S[d] = (d < dim && col && !fresh) ? slot[(int64_t)d * vdim + c] : 0.f;
+  for (int d = tid; d < ML_MAXD; d += ML_COLS) { nv[d] = (d < dim && !fresh) ? slot[(int64_t)dim * vdim + d] : 0.f; ks[d] = 0.f; qs[d] = 0.f; }
+  float m = fresh ? 0.f : slot[(int64_t)dim * vdim + dim];
+  const E *qp = (const E*)a.q, *kp = (const E*)a.k, *vp = (const E*)a.v;
+  __syncthreads();
+  for (int t = rs; t < re; ++t) {
+    for (int d = tid; d < dim; d += ML_COLS) {
+      ks[d] = ldf(kp + (int64_t)t * a.ld + h * dim + d);
+      qs[d] = ldf(qp + (int64_t)t * a.ld + h * dim + d) * a.q_scale;
+    }
+    const float ip = a.gates[(int64_t)t * 2 * a.H + h], fp = a.gates[(int64_t)t * 2 * a.H + a.H + h];
+    const float it = a.cap * tanhf(ip / a.cap);
+    const float fc = a.cap * tanhf(fp / a.cap);
+    const float ft = fminf(fc, 0.f) - log1pf(expf(-fabsf(fc)));          // logsigmoid
+    const float mn = fmaxf(ft + m, it);
+    const float fa = expf(ft + m - mn), ia = expf(it - mn);
+    m = mn;
+    const float vv = col ? ia * ldf(vp + (int64_t)t * a.ld + h * vdim + c) : 0.f;
+    __syncthreads();
+    if (tid < 32) {
+      float part = 0.f;
+      for (int d = tid; d < dim; d += 32) {
+        const float nn = fmaf(fa, nv[d], ia * ks[d]);
+        nv[d] = nn;
+        part = fmaf(nn, qs[d], part);
+      }
+      part = warp_sum(part);
+      if (tid == 0) nq_s = part;
+    }
+    float num = 0.f;
+#pragma unroll
+    for (int d4 = 0; d4 < ML_MAXD / 4; ++d4) {
+      if (d4 * 4 < dim) {                        // dim is a multiple of 4 on this path; ks / qs are zero beyond it anyway
+        const float4 k4 = reinterpret_cast<const float4*>(ks)[d4], q4 = reinterpret_cast<const float4*>(qs)[d4];
+        S[d4 * 4 + 0] = fmaf(fa, S[d4 * 4 + 0], k4.x * vv); num = fmaf(S[d4 * 4 + 0], q4.x, num);
+        S[d4 * 4 + 1] = fmaf(fa, S[d4 * 4 + 1], k4.y * vv); num = fmaf(S[d4 * 4 + 1], q4.y, num);
+        S[d4 * 4 + 2] = fmaf(fa, S[d4 * 4 + 2], k4.z * vv); num = fmaf(S[d4 * 4 + 2], q4.z, num);
+        S[d4 * 4 + 3] = fmaf(fa, S[d4 * 4 + 3], k4.w * vv); num = fmaf(S[d4 * 4 + 3], q4.w, num);
+      }
+    }
+    __syncthreads();
+    if (col) a.o_scratch[(int64_t)t * a.H * vdim + h * vdim + c] = num / (fmaxf(fabsf(nq_s), expf(-m)) + a.den_eps);
+  }
+  if (col) {
+#pragma unroll
+    for (int d = 0; d < ML_MAXD; ++d) if (d < dim) slot[(int64_t)d * vdim + c] = S[d];
+  }
+  if (blockIdx.z == 0) {
+    __syncthreads();
+    for (int d = tid; d < dim; d += ML_COLS) slot[(int64_t)dim * vdim + d] = nv[d];
+    if (tid == 0) slot[(int64_t)dim * vdim + dim] = m;
+  }
+}
+
+template <typename E>
+__global__ void mlstm_norm_gate_kernel(MlstmArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[33];
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* o = a.o_scratch + (int64_t)t * a.H * a.vdim + h * a.vdim;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) ss = fmaf(o[c], o[c], ss);
+  ss = block_sum(ss, red);
+  const float inv = a.out_scale / sqrtf(ss / (float)a.vdim + a.eps);
+  for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
+    const float gate = 1.f / (1.f + expf(-ldf((const E*)a.g + (int64_t)t * a.ld + h * a.vdim + c)));
+    stf((E*)a.out + (int64_t)t * a.ldo + h * a.vdim + c, o[c] * inv * ldf((const E*)a.norm_w + h * a.vdim + c) * gate);
+  }
+}
+
 int mlstm_step(const MlstmArgs& a, cudaStream_t st) {
   if (a.T <= 0 || a.B <= 0) return 0;
+  if (a.o_scratch && a.dim <= ML_MAXD && a.dim % 4 == 0 && a.H <= 65535) {
+    const dim3 grid(a.B, a.H, (a.vdim + ML_COLS - 1) / ML_COLS), g2(a.T, a.H);
+    const int nt = std::min(256, (a.vdim + 31) / 32 * 32);
+    if (a.elt == KGE_ELT_F32) {
+      KGE_CUDA_OK(launch_pdl(mlstm_cols_kernel<float>, grid, dim3(ML_COLS), 0, st, a));
+      KGE_CUDA_OK(launch_pdl(mlstm_norm_gate_kernel<float>, g2, dim3(nt), 0, st, a));
+    } else {
+      KGE_CUDA_OK(launch_pdl(mlstm_cols_kernel<__nv_bfloat16>, grid, dim3(ML_COLS), 0, st, a));
+      KGE_CUDA_OK(launch_pdl(mlstm_norm_gate_kernel<__nv_bfloat16>, g2, dim3(nt), 0, st, a));
+    }
+    return 0;
+  }
   const int threads = (std::max(a.dim, a.vdim) + 31) / 32 * 32;
   KGE_REQUIRE(threads <= 1024, "mlstm_step: head sizes %d x %d need more than 1024 threads", a.dim, a.vdim);
   const size_t smem = ((size_t)a.dim * a.vdim + 3 * (size_t)a.dim + 64) * 4;

@@ -157,11 +157,13 @@ def test_pages_and_slots_are_used_again(kge, tmp_path):
         check(got[r], want[r], "float32", f"request {r}")
 
 
+@pytest.mark.parametrize("dims", [(12, 20), (32, 40)])       # the per-row kernel; the tensor-core kernel (bfloat16, key size a multiple of 16)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_chunk_edges_with_peaked_scores(kge, tmp_path, dtype):
+def test_chunk_edges_with_peaked_scores(kge, tmp_path, dtype, dims):
     """Attention alone, scores large enough that single keys carry most of the weight: a key that is wrongly seen or
     missed at a chunk's edge, or a page border that is misread, moves the logits far beyond rounding."""
-    cfg = oh.make_config(layers=("parallel",), mlps=(None,), right_scale=0.0, chunk=21, scale=1.6, heads=4, kv_heads=1, dim=12, vdim=20)
+    cfg = oh.make_config(layers=("parallel",), mlps=(None,), right_scale=0.0, chunk=21, scale=1.6 * (12 / dims[0]) ** 0.5, heads=4, kv_heads=1,
+                         dim=dims[0], vdim=dims[1])
     W = oh.make_weights(cfg, seed=9)
     toks = prompt(cfg, 70, 30)
     want = oh.forward(cfg, W, toks)
@@ -173,6 +175,18 @@ def test_chunk_edges_with_peaked_scores(kge, tmp_path, dtype):
     check(run_pieces(llm, 1, toks, [19] + [1] * 30 + [21]), want, dtype, "decoding over two edges")
     check(run_pieces(llm, 2, toks, [20, 2, 20, 2, 26]), want, dtype, "pieces that straddle the edges")
     llm.close()
+
+
+def test_far_keys_tensor_core_kernel(kge, tmp_path):
+    """bfloat16, 48-wide heads, several key tiles per warp and a chunk edge in the middle of the prompt; grouped heads."""
+    cfg = oh.make_config(layers=("parallel",), mlps=(None,), right_scale=0.0, chunk=200, scale=0.6, heads=6, kv_heads=2, dim=48, vdim=48)
+    W = oh.make_weights(cfg, seed=15)
+    toks = prompt(cfg, 290, 32)
+    want = oh.forward(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", bs=64)
+    got = np.concatenate([run_pieces(llm, 0, toks[:150], [150]), run_pieces(llm, 0, toks[150:260], [3, 45, 2, 60]), run_pieces(llm, 0, toks[260:], [1] * 30)])
+    llm.close()
+    check(got, want, "bfloat16")
 
 
 def test_far_keys_among_hundreds(kge, tmp_path):
