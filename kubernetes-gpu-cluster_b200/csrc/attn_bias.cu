@@ -96,19 +96,23 @@ __device__ __forceinline__ uint32_t pack2raw(__nv_bfloat16 lo, __nv_bfloat16 hi)
   return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
 }
 
-__global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasArgs a) {
+// ROWS = false: a CTA owns 16 rows and its warps split the key tiles (decoding, short pieces).  ROWS = true: a CTA owns
+// 64 rows, 16 per warp, and every key tile is staged once for all four warps (prompts).
+template <bool ROWS>
+__global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasArgs a, int req0) {
   pdl_launch_dependents();
   pdl_wait();
   typedef __nv_bfloat16 E;
   extern __shared__ __align__(16) unsigned char am_smem[];
-  const int b = blockIdx.z, g = blockIdx.y, hpg = a.H / a.G;
-  const int rs = a.qsl[b], nrows = (a.qsl[b + 1] - rs) * hpg, R0 = blockIdx.x * 16;
-  if (R0 >= nrows) return;
+  const int b = req0 + blockIdx.z, g = blockIdx.y, hpg = a.H / a.G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, qr = lane >> 2, qc = (lane & 3) * 2;
+  const int rs = a.qsl[b], nrows = (a.qsl[b + 1] - rs) * hpg, Rc = blockIdx.x * (ROWS ? 16 * AM_WARPS : 16);
+  if (Rc >= nrows) return;
+  const int R0 = ROWS ? Rc + warp * 16 : Rc;               // may lie beyond the request's rows: such a warp only helps staging
   const int dim = a.dim, vdim = a.vdim, ksteps = dim >> 4, vtiles = vdim >> 3;
   const int kst = dim + AM_PAD, vst = vdim + AM_PAD;                 // shared row strides (elements)
   const size_t region = (size_t)AM_KT * (kst + vst) * sizeof(E);
-  E* Ks = reinterpret_cast<E*>(am_smem + warp * region);
+  E* Ks = reinterpret_cast<E*>(am_smem + (ROWS ? 0 : warp) * region);
   E* Vs = Ks + AM_KT * kst;
   // this thread's two rows: qr and qr + 8 of the tile
   int pos[2], lo[2], tok[2], head[2];
@@ -124,9 +128,15 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
     lo[h] = (a.chunk > 0 && pos[h] >= 0) ? (pos[h] / a.chunk) * a.chunk : 0;
     slope2[h] = a.bias_span > 0.f ? exp2f(-a.bias_span * (float)(head[h] + 1) / (float)a.H) * log2e : 0.f;
   }
-  const int pos_first = a.positions[rs + R0 / hpg], pos_last = a.positions[rs + min(R0 + 15, nrows - 1) / hpg];
+  const int pos_first = a.positions[rs + Rc / hpg], pos_last = a.positions[rs + min(Rc + (ROWS ? 16 * AM_WARPS : 16) - 1, nrows - 1) / hpg];
   const int lo_min = a.chunk > 0 ? (pos_first / a.chunk) * a.chunk : 0;
   const int ntiles = (pos_last - lo_min + AM_KT) / AM_KT;
+  // the keys this warp's own rows can see (ROWS: tiles outside are staged for the others but not computed here)
+  // (the same for every lane of the warp: the mma instructions below need all 32 lanes on one path)
+  const bool wany = R0 < nrows;
+  const int own_hi = wany ? a.positions[rs + min(R0 + 15, nrows - 1) / hpg] : -1;
+  const int own_first = wany ? a.positions[rs + R0 / hpg] : 0;
+  const int own_lo = a.chunk > 0 ? (own_first / a.chunk) * a.chunk : 0;
   const float scale2 = a.scale * log2e;
   uint32_t qf[AM_MAXD / 16][4];
 #pragma unroll
@@ -150,26 +160,31 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
   const E* kc = (const E*)a.k_cache;
   const E* vc = (const E*)a.v_cache;
   const int kseg = dim >> 3, vseg = vdim >> 3;
-  for (int kt = warp; kt < ntiles; kt += AM_WARPS) {
+  for (int kt = ROWS ? 0 : warp; kt < ntiles; kt += ROWS ? 1 : AM_WARPS) {
     const int j0 = lo_min + kt * AM_KT;
+    if (ROWS) __syncthreads();                              // the previous tile has been read by every warp
     // stage the tile: lane i knows where key j0 + i lives; the 16-byte pieces of a row are fetched by consecutive lanes
     const int jl = j0 + lane;
     const int64_t myrow = jl <= pos_last ? ((int64_t)bt[jl / a.block_size] * a.G + g) * a.block_size + jl % a.block_size : -1;
-    for (int idx = lane; idx < AM_KT * kseg; idx += 32) {
+    const int sid = ROWS ? threadIdx.x : lane, sstep = ROWS ? AM_WARPS * 32 : 32;
+    for (int idx0 = 0; idx0 < AM_KT * kseg; idx0 += sstep) {       // whole warps run the loop: the shuffle needs every lane
+      const int idx = min(idx0 + sid, AM_KT * kseg - 1);
       const int key = idx / kseg, seg = idx % kseg;
       const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (row >= 0) v = *reinterpret_cast<const uint4*>(kc + row * dim + seg * 8);
       *reinterpret_cast<uint4*>(Ks + key * kst + seg * 8) = v;
     }
-    for (int idx = lane; idx < AM_KT * vseg; idx += 32) {
+    for (int idx0 = 0; idx0 < AM_KT * vseg; idx0 += sstep) {
+      const int idx = min(idx0 + sid, AM_KT * vseg - 1);
       const int key = idx / vseg, seg = idx % vseg;
       const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (row >= 0) v = *reinterpret_cast<const uint4*>(vc + row * vdim + seg * 8);
       *reinterpret_cast<uint4*>(Vs + key * vst + seg * 8) = v;
     }
-    __syncwarp();
+    if (ROWS) __syncthreads(); else __syncwarp();
+    if (ROWS && (j0 > own_hi || j0 + AM_KT <= own_lo)) continue;
     float sacc[4][4];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
@@ -234,14 +249,27 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
         }
       }
     }
-    __syncwarp();
+    if (!ROWS) __syncwarp();
   }
-  // merge the four warps' partial results
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
   }
+  if (ROWS) {
+    // each warp finished its own rows: normalise and store from the registers
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (pos[h] < 0) continue;
+      const float inv = a.out_scale / l[h];
+      E* out = (E*)a.out + (int64_t)tok[h] * a.ldo + head[h] * vdim + qc;
+#pragma unroll
+      for (int v = 0; v < AM_MAXD / 8; ++v)
+        if (v < vtiles) *reinterpret_cast<uint32_t*>(out + v * 8) = pack2(o[v][2 * h] * inv, o[v][2 * h + 1] * inv);
+    }
+    return;
+  }
+  // merge the four warps' partial results
   __syncthreads();                                          // every warp is done with its tiles: the regions are free
   float* Os = reinterpret_cast<float*>(am_smem + warp * region);      // [16][vdim]
   float* ML = reinterpret_cast<float*>(am_smem + AM_WARPS * region);  // [warps][2][16]
@@ -285,11 +313,20 @@ int attn_bias_chunk(const AttnBiasArgs& a, cudaStream_t st) {
     const size_t smem = (size_t)AM_WARPS * AM_KT * (a.dim + a.vdim + 2 * AM_PAD) * 2 + (size_t)AM_WARPS * 2 * 16 * 4;
     static size_t smem_set = 0;                       // opt in once per size that needs more than the default 48 KB
     if (smem > 48 * 1024 && smem > smem_set) {
-      KGE_CUDA_OK(cudaFuncSetAttribute(attn_bias_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      KGE_CUDA_OK(cudaFuncSetAttribute(attn_bias_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      KGE_CUDA_OK(cudaFuncSetAttribute(attn_bias_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       smem_set = smem;
     }
-    const dim3 grid((a.max_q * hpg + 15) / 16, a.G, a.B);
-    KGE_CUDA_OK(launch_pdl(attn_bias_mma_kernel, grid, dim3(AM_WARPS * 32), smem, st, a));
+    // the leading one-token requests, then the rest; 64-row CTAs where a request has that many rows and its output
+    // pairs can be stored as 32-bit words
+    const int D = std::min(std::max(a.num_decode, 0), a.B);
+    if (D > 0) KGE_CUDA_OK(launch_pdl(attn_bias_mma_kernel<false>, dim3((hpg + 15) / 16, a.G, D), dim3(AM_WARPS * 32), smem, st, a, 0));
+    if (D < a.B) {
+      const int rows = a.max_q * hpg;
+      const bool wide = rows > 32 && a.ldo % 2 == 0 && a.vdim % 2 == 0 && (reinterpret_cast<uintptr_t>(a.out) & 3) == 0;
+      if (wide) KGE_CUDA_OK(launch_pdl(attn_bias_mma_kernel<true>, dim3((rows + 16 * AM_WARPS - 1) / (16 * AM_WARPS), a.G, a.B - D), dim3(AM_WARPS * 32), smem, st, a, D));
+      else KGE_CUDA_OK(launch_pdl(attn_bias_mma_kernel<false>, dim3((rows + 15) / 16, a.G, a.B - D), dim3(AM_WARPS * 32), smem, st, a, D));
+    }
     return 0;
   }
   KGE_REQUIRE(a.vdim <= 32 * ATT_MAXV, "attn_bias_chunk: value head size %d > %d", a.vdim, 32 * ATT_MAXV);

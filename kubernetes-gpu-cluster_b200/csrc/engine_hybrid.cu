@@ -367,6 +367,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       aa.B = B; aa.T = T; aa.H = h.heads; aa.G = h.kv_heads; aa.dim = h.dim; aa.vdim = h.vdim; aa.block_size = bs; aa.chunk = h.chunk;
       aa.scale = h.scale; aa.bias_span = 8.f; aa.out_scale = h.left_scale; aa.elt = elt;
       for (int r = 0; r < B; ++r) aa.max_q = std::max(aa.max_q, hm.qsl[r + 1] - hm.qsl[r]);
+      while (aa.num_decode < B && hm.qsl[aa.num_decode + 1] - hm.qsl[aa.num_decode] == 1) ++aa.num_decode;
       double keys = 0;                                   // visible keys over all rows
       for (int t = 0; t < T; ++t) keys += h.chunk > 0 ? hm.pos[t] % h.chunk + 1 : hm.pos[t] + 1;
       HFWD(decode_only ? C_ATT_DEC : C_ATT_GEN, (decode_only ? keys : (double)T) * h.kv_heads * (h.dim + h.vdim) * es + (double)T * h.heads * (h.dim + h.vdim) * es,

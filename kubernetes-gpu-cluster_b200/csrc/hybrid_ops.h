@@ -62,6 +62,8 @@ struct AttnBiasArgs {
   const int32_t* token_req = nullptr;      // [T] request index of every token row
   int B = 0, T = 0, H = 0, G = 0, dim = 0, vdim = 0, block_size = 0, chunk = 0;
   int max_q = 0;                           // the longest request's rows in this step (0 = unknown: the per-row kernel runs)
+  int num_decode = 0;                      // leading requests that bring one token each: their keys are split over a CTA's warps,
+                                           // while requests with many rows give each warp 16 rows of a shared key tile
   float scale = 1.f, bias_span = 0.f, out_scale = 1.f;
   int elt = KGE_ELT_BF16;
 };

@@ -109,11 +109,13 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// eight consecutive k of one row into a shared tile, zero beyond K or for a missing row; 16-byte load when aligned
-__device__ __forceinline__ void stage8(__nv_bfloat16* dst, const __nv_bfloat16* row, int k, int K, bool vec) {
-  if (row && vec && k + 8 <= K) { *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(row + k); return; }
+// eight consecutive k of one row as one 16-byte register, zero beyond K or for a missing row; one 16-byte load when aligned
+__device__ __forceinline__ uint4 load8(const __nv_bfloat16* row, int k, int K, bool vec) {
+  if (row && vec && k + 8 <= K) return *reinterpret_cast<const uint4*>(row + k);
+  union { uint4 v; __nv_bfloat16 e[8]; } u;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) dst[i] = (row && k + i < K) ? row[k + i] : __float2bfloat16_rn(0.f);
+  for (int i = 0; i < 8; ++i) u.e[i] = (row && k + i < K) ? row[k + i] : __float2bfloat16_rn(0.f);
+  return u.v;
 }
 
 template <typename O, bool DUAL>
@@ -144,11 +146,19 @@ __global__ void __launch_bounds__(256) linear_mma_kernel(LinearArgs a) {
   const bool xvec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && a.ldx % 8 == 0;
   const bool wvec = ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && a.K % 8 == 0 && (!DUAL || (reinterpret_cast<uintptr_t>(w2) & 15) == 0);
   float acc[2][2][4] = {}, acc2[DUAL ? 2 : 1][2][4] = {};
+  // the next k-tile travels from global memory to registers while the tensor cores work on the current one
+  uint4 px = load8(xrow, sk, a.K, xvec), pw = load8(wrow, sk, a.K, wvec), pw2 = make_uint4(0u, 0u, 0u, 0u);
+  if (DUAL) pw2 = load8(w2row, sk, a.K, wvec);
   for (int k0 = 0; k0 < a.K; k0 += MBK) {
-    stage8(&xs[sr][sk], xrow, k0 + sk, a.K, xvec);
-    stage8(&ws[sr][sk], wrow, k0 + sk, a.K, wvec);
-    if (DUAL) stage8(&ws2[sr][sk], w2row, k0 + sk, a.K, wvec);
+    *reinterpret_cast<uint4*>(&xs[sr][sk]) = px;
+    *reinterpret_cast<uint4*>(&ws[sr][sk]) = pw;
+    if (DUAL) *reinterpret_cast<uint4*>(&ws2[sr][sk]) = pw2;
     __syncthreads();
+    if (k0 + MBK < a.K) {
+      px = load8(xrow, k0 + MBK + sk, a.K, xvec);
+      pw = load8(wrow, k0 + MBK + sk, a.K, wvec);
+      if (DUAL) pw2 = load8(w2row, k0 + MBK + sk, a.K, wvec);
+    }
 #pragma unroll
     for (int ks = 0; ks < MBK / 16; ++ks) {
       const int kc = ks * 16 + (lane & 3) * 2;

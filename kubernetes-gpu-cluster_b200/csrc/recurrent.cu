@@ -63,14 +63,30 @@ __global__ void __launch_bounds__(128) rglru_scan_kernel(RglruArgs a) {
   E* out = (E*)a.out;
   const float sp = a.decay_c * softplusf_(ldf((const E*)a.lam + c));
   float S = p0 > 0 ? slot[c] : 0.f;
-  for (int t = rs; t < re; ++t) {
-    const float r = sigmoidf_(a.gates[(int64_t)t * 2 * a.width + c]);
-    const float i = sigmoidf_(a.gates[(int64_t)t * 2 * a.width + a.width + c]);
-    const float log_a = -sp * r;
-    const float av = expf(log_a);
-    const float mult = sqrtf(-expm1f(2.f * log_a));          // sqrt(1 - a^2) without cancellation near a = 1
-    S = fmaf(av, S, mult * i * ldf(u + (int64_t)t * a.width + c));
-    stf(out + (int64_t)t * a.width + c, S * gelu_tanhf_(ldf(yx + (int64_t)t * 2 * a.width + c)));
+  // eight tokens at a time: all their operands are requested before the first is used, so the recurrence itself - one
+  // dependent fma per token - is what the loop waits for, not a memory round trip per token
+  constexpr int G = 8;
+  for (int t0 = rs; t0 < re; t0 += G) {
+    float gr[G], gi[G], uv[G], yv[G];
+#pragma unroll
+    for (int k = 0; k < G; ++k) {
+      const int t = min(t0 + k, re - 1);
+      gr[k] = a.gates[(int64_t)t * 2 * a.width + c];
+      gi[k] = a.gates[(int64_t)t * 2 * a.width + a.width + c];
+      uv[k] = ldf(u + (int64_t)t * a.width + c);
+      yv[k] = ldf(yx + (int64_t)t * 2 * a.width + c);
+    }
+#pragma unroll
+    for (int k = 0; k < G; ++k) {
+      if (t0 + k < re) {
+        const float r = sigmoidf_(gr[k]), i = sigmoidf_(gi[k]);
+        const float log_a = -sp * r;
+        const float av = expf(log_a);
+        const float mult = sqrtf(-expm1f(2.f * log_a));          // sqrt(1 - a^2) without cancellation near a = 1
+        S = fmaf(av, S, mult * i * uv[k]);
+        stf(out + (int64_t)(t0 + k) * a.width + c, S * gelu_tanhf_(yv[k]));
+      }
+    }
   }
   slot[c] = S;
   // the conv's next inputs: positions p1 - (taps - 1) .. p1 - 1 with p1 = p0 + n, from this step's rows or the old tail
@@ -170,61 +186,85 @@ __global__ void mlstm_step_kernel(MlstmArgs a) {
 // state in registers (dim <= 128), the first warp keeps the normaliser n, and the un-normalised read-out goes to an fp32
 // scratch; mlstm_norm_gate_kernel then divides each head by its root mean square and applies weight and output gate.
 // More blocks than (request, head) pairs fill the machine when few requests prefill, and the state never sits in shared memory.
-constexpr int ML_MAXD = 128, ML_COLS = 64;
+constexpr int ML_MAXD = 128, ML_COLS = 64, ML_THREADS = ML_COLS + 32;      // two warps of value columns, one for the normaliser
+
+// gate pre-activations -> log gates, in place, for every token at once (the recurrence then needs two exponentials a token)
+__global__ void mlstm_log_gates_kernel(float* gates, int T, int H, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * 2 * H) return;
+  const float c = cap * tanhf(gates[i] / cap);
+  gates[i] = (i % (2 * H)) < H ? c : fminf(c, 0.f) - log1pf(expf(-fabsf(c)));     // input gate | logsigmoid for the forget gate
+}
 
 template <typename E>
-__global__ void __launch_bounds__(ML_COLS) mlstm_cols_kernel(MlstmArgs a) {
+__global__ void __launch_bounds__(ML_THREADS) mlstm_cols_kernel(MlstmArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ __align__(16) float ks[ML_MAXD], qs[ML_MAXD], nv[ML_MAXD];
   __shared__ float nq_s;
   const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, c = blockIdx.z * ML_COLS + tid;
   const int dim = a.dim, vdim = a.vdim;
-  const bool col = c < vdim;
+  const bool colw = tid < ML_COLS;                 // a value-column thread (the last warp keeps n instead)
+  const bool col = colw && c < vdim;
   const int rs = a.qsl[b], re = a.qsl[b + 1], p0 = a.positions[rs];
   float* slot = a.state + (int64_t)a.slots[b] * a.slot_stride + (int64_t)h * ((int64_t)dim * vdim + dim + 1);
   const bool fresh = p0 == 0;
   float S[ML_MAXD];
 #pragma unroll
   for (int d = 0; d < ML_MAXD; ++d) S[d] = (d < dim && col && !fresh) ? slot[(int64_t)d * vdim + c] : 0.f;
-  for (int d = tid; d < ML_MAXD; d += ML_COLS) { nv[d] = (d < dim && !fresh) ? slot[(int64_t)dim * vdim + d] : 0.f; ks[d] = 0.f; qs[d] = 0.f; }
+  for (int d = tid; d < ML_MAXD; d += ML_THREADS) { nv[d] = (d < dim && !fresh) ? slot[(int64_t)dim * vdim + d] : 0.f; ks[d] = 0.f; qs[d] = 0.f; }
   float m = fresh ? 0.f : slot[(int64_t)dim * vdim + dim];
   const E *qp = (const E*)a.q, *kp = (const E*)a.k, *vp = (const E*)a.v;
   __syncthreads();
-  for (int t = rs; t < re; ++t) {
-    for (int d = tid; d < dim; d += ML_COLS) {
-      ks[d] = ldf(kp + (int64_t)t * a.ld + h * dim + d);
-      qs[d] = ldf(qp + (int64_t)t * a.ld + h * dim + d) * a.q_scale;
+  // operands of the NEXT token are requested while the current one is computed (two key / query entries per thread)
+  float kn[2], qn[2], vn, ipn, fpn;
+  auto fetch = [&](int t) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int d = tid + j * ML_COLS;
+      kn[j] = (colw && d < dim) ? ldf(kp + (int64_t)t * a.ld + h * dim + d) : 0.f;
+      qn[j] = (colw && d < dim) ? ldf(qp + (int64_t)t * a.ld + h * dim + d) * a.q_scale : 0.f;
     }
-    const float ip = a.gates[(int64_t)t * 2 * a.H + h], fp = a.gates[(int64_t)t * 2 * a.H + a.H + h];
-    const float it = a.cap * tanhf(ip / a.cap);
-    const float fc = a.cap * tanhf(fp / a.cap);
-    const float ft = fminf(fc, 0.f) - log1pf(expf(-fabsf(fc)));          // logsigmoid
+    vn = col ? ldf(vp + (int64_t)t * a.ld + h * vdim + c) : 0.f;
+    ipn = a.gates[(int64_t)t * 2 * a.H + h];
+    fpn = a.gates[(int64_t)t * 2 * a.H + a.H + h];
+  };
+  if (rs < re) fetch(rs);
+  for (int t = rs; t < re; ++t) {
+    if (colw) { ks[tid] = kn[0]; ks[tid + ML_COLS] = kn[1]; qs[tid] = qn[0]; qs[tid + ML_COLS] = qn[1]; }
+    const float it = ipn, ft = fpn, vcur = vn;     // log gates (mlstm_log_gates_kernel ran before)
+    if (t + 1 < re) fetch(t + 1);
     const float mn = fmaxf(ft + m, it);
     const float fa = expf(ft + m - mn), ia = expf(it - mn);
     m = mn;
-    const float vv = col ? ia * ldf(vp + (int64_t)t * a.ld + h * vdim + c) : 0.f;
+    const float vv = ia * vcur;
     __syncthreads();
-    if (tid < 32) {
+    float num = 0.f;
+    if (!colw) {
+      const int ln = tid - ML_COLS;
       float part = 0.f;
-      for (int d = tid; d < dim; d += 32) {
+      for (int d = ln; d < dim; d += 32) {
         const float nn = fmaf(fa, nv[d], ia * ks[d]);
         nv[d] = nn;
         part = fmaf(nn, qs[d], part);
       }
       part = warp_sum(part);
-      if (tid == 0) nq_s = part;
-    }
-    float num = 0.f;
+      if (ln == 0) nq_s = part;
+    } else {
+      float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f;       // four chains: the read-out does not wait on one long dependency
 #pragma unroll
-    for (int d4 = 0; d4 < ML_MAXD / 4; ++d4) {
-      if (d4 * 4 < dim) {                        // dim is a multiple of 4 on this path; ks / qs are zero beyond it anyway
-        const float4 k4 = reinterpret_cast<const float4*>(ks)[d4], q4 = reinterpret_cast<const float4*>(qs)[d4];
-        S[d4 * 4 + 0] = fmaf(fa, S[d4 * 4 + 0], k4.x * vv); num = fmaf(S[d4 * 4 + 0], q4.x, num);
-        S[d4 * 4 + 1] = fmaf(fa, S[d4 * 4 + 1], k4.y * vv); num = fmaf(S[d4 * 4 + 1], q4.y, num);
-        S[d4 * 4 + 2] = fmaf(fa, S[d4 * 4 + 2], k4.z * vv); num = fmaf(S[d4 * 4 + 2], q4.z, num);
-        S[d4 * 4 + 3] = fmaf(fa, S[d4 * 4 + 3], k4.w * vv); num = fmaf(S[d4 * 4 + 3], q4.w, num);
+      for (int d4 = 0; d4 < ML_MAXD / 4; ++d4) {
+        if (d4 * 4 < dim) {                      // dim is a multiple of 4 on this path
+          const float4 k4 = reinterpret_cast<const float4*>(ks)[d4], q4 = reinterpret_cast<const float4*>(qs)[d4];
+          S[d4 * 4 + 0] = fmaf(fa, S[d4 * 4 + 0], k4.x * vv); n0 = fmaf(S[d4 * 4 + 0], q4.x, n0);
+          S[d4 * 4 + 1] = fmaf(fa, S[d4 * 4 + 1], k4.y * vv); n1 = fmaf(S[d4 * 4 + 1], q4.y, n1);
+          S[d4 * 4 + 2] = fmaf(fa, S[d4 * 4 + 2], k4.z * vv); n2 = fmaf(S[d4 * 4 + 2], q4.z, n2);
+          S[d4 * 4 + 3] = fmaf(fa, S[d4 * 4 + 3], k4.w * vv); n3 = fmaf(S[d4 * 4 + 3], q4.w, n3);
+        }
       }
+      num = (n0 + n1) + (n2 + n3);
     }
     __syncthreads();
     if (col) a.o_scratch[(int64_t)t * a.H * vdim + h * vdim + c] = num / (fmaxf(fabsf(nq_s), expf(-m)) + a.den_eps);
@@ -235,7 +275,7 @@ __global__ void __launch_bounds__(ML_COLS) mlstm_cols_kernel(MlstmArgs a) {
   }
   if (blockIdx.z == 0) {
     __syncthreads();
-    for (int d = tid; d < dim; d += ML_COLS) slot[(int64_t)dim * vdim + d] = nv[d];
+    for (int d = tid; d < dim; d += ML_THREADS) slot[(int64_t)dim * vdim + d] = nv[d];
     if (tid == 0) slot[(int64_t)dim * vdim + dim] = m;
   }
 }
@@ -262,11 +302,12 @@ int mlstm_step(const MlstmArgs& a, cudaStream_t st) {
   if (a.o_scratch && a.dim <= ML_MAXD && a.dim % 4 == 0 && a.H <= 65535) {
     const dim3 grid(a.B, a.H, (a.vdim + ML_COLS - 1) / ML_COLS), g2(a.T, a.H);
     const int nt = std::min(256, (a.vdim + 31) / 32 * 32);
+    KGE_CUDA_OK(launch_pdl(mlstm_log_gates_kernel, dim3((a.T * 2 * a.H + 255) / 256), dim3(256), 0, st, const_cast<float*>(a.gates), a.T, a.H, a.cap));
     if (a.elt == KGE_ELT_F32) {
-      KGE_CUDA_OK(launch_pdl(mlstm_cols_kernel<float>, grid, dim3(ML_COLS), 0, st, a));
+      KGE_CUDA_OK(launch_pdl(mlstm_cols_kernel<float>, grid, dim3(ML_THREADS), 0, st, a));
       KGE_CUDA_OK(launch_pdl(mlstm_norm_gate_kernel<float>, g2, dim3(nt), 0, st, a));
     } else {
-      KGE_CUDA_OK(launch_pdl(mlstm_cols_kernel<__nv_bfloat16>, grid, dim3(ML_COLS), 0, st, a));
+      KGE_CUDA_OK(launch_pdl(mlstm_cols_kernel<__nv_bfloat16>, grid, dim3(ML_THREADS), 0, st, a));
       KGE_CUDA_OK(launch_pdl(mlstm_norm_gate_kernel<__nv_bfloat16>, g2, dim3(nt), 0, st, a));
     }
     return 0;
