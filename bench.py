@@ -594,6 +594,7 @@ def run_designs(args):
                 llm = kge.LLM(d, load_format="dummy", seed=1, dtype="bfloat16", block_size=bs, max_model_len=ctx + 64, max_num_seqs=B,
                               max_num_batched_tokens=PB * ctx, num_gpu_blocks_override=B * ((ctx + bs) // bs) + 2, enable_prefix_caching=False)
             rec = {"weight_gb": llm.weight_bytes / 1e9}
+            log(f"designs {name} {arm}: engine up, {rec['weight_gb']:.2f} GB of weights")
             pre = raw_batch(PB, ctx, ctx, bs, z["vocab"], 1)
             dec = raw_batch(B, ctx, 1, bs, z["vocab"], 2)
             for r0 in range(0, B, PB):           # fill every request's cache and state first
@@ -601,8 +602,10 @@ def run_designs(args):
                 sub = dict(ids=fill["ids"][r0 * ctx:(r0 + PB) * ctx], pos=fill["pos"][:PB * ctx], qsl=fill["qsl"][:PB + 1],
                            seq_lens=fill["seq_lens"][:PB], btab=fill["btab"][r0:r0 + PB], slots=fill["slots"][r0 * ctx:(r0 + PB) * ctx], rows=fill["rows"][:PB])
                 time_raw_steps(kge, llm, sub, 1, 0)
+            log(f"designs {name} {arm}: caches and states filled")
             for phase, batch, ntok in (("prefill", pre, PB * ctx), ("decode", dec, B)):
                 sec = time_raw_steps(kge, llm, batch, args.steps, max(3, args.warmup))
+                log(f"designs {name} {arm}: {phase} {sec * 1e3:.2f} ms per step")
                 llm.set_timing(True)
                 time_raw_steps(kge, llm, batch, 1, 0)
                 stats = llm.kernel_stats()

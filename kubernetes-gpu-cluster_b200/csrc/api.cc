@@ -30,10 +30,12 @@ bool pdl_enabled() {
 void pdl_set_enabled(bool on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
 static thread_local bool g_pdl_break = false;
 void pdl_break_next() { g_pdl_break = true; }
+static thread_local int g_pdl_suspended = 0;
+void pdl_suspend(bool on) { g_pdl_suspended += on ? 1 : -1; }
 bool pdl_for_this_launch() {
   const bool brk = g_pdl_break;
   g_pdl_break = false;
-  return pdl_enabled() && !brk;
+  return pdl_enabled() && !brk && g_pdl_suspended <= 0;
 }
 
 static std::atomic<int> g_tun[TUN_COUNT] = {{1}, {0}, {0}, {0}, {1}, {0}, {1}, {0}, {1}, {1}};   // even grid measured +6.5 % on the C3 gate_up GEMM (profiles/r01_knob_sweep.md)

@@ -5,6 +5,8 @@
 // and runs its step: the same flattened batch, block tables and slot mapping as every other model, plus a state slot
 // per request.  Nothing here depends on how a prompt was cut into steps: recurrences continue from the slot, attention
 // reads the paged cache, and every other operation is per row.
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -283,6 +285,8 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
 
 enum { C_GEMM_S = 0, C_GEMM_L = 1, C_ATT_DEC = 2, C_ATT_GEN = 3, C_NORM = 4, C_KVW = 5, C_ACT = 6, C_EMBED = 7, C_SAMPLE = 8, C_RGLRU = 10, C_MLSTM = 11, C_MOE = 12 };
 
+// KGE_TRACE_LAUNCHES=1 (diagnostics): synchronise after every launch of a step and name it on stderr
+static const bool g_trace_launches = getenv("KGE_TRACE_LAUNCHES") != nullptr;
 #define HFWD(cat, bytes, flops, call)      \
   do {                                     \
     timer_begin(e, cat, bytes, flops);     \
@@ -290,6 +294,11 @@ enum { C_GEMM_S = 0, C_GEMM_L = 1, C_ATT_DEC = 2, C_ATT_GEN = 3, C_NORM = 4, C_K
     if (_rc) return _rc;                   \
     timer_end(e);                          \
     ++e->launches;                         \
+    if (g_trace_launches) {                \
+      fprintf(stderr, "[kge] %s ...", #call); fflush(stderr);                                 \
+      const cudaError_t _ce = cudaStreamSynchronize(e->stream);                                \
+      fprintf(stderr, " %s\n", cudaGetErrorString(_ce)); fflush(stderr);                       \
+    }                                      \
   } while (0)
 
 // y[T, N] = act(x[T, K] w^T + b) in the engine's storage type (fp32 output where asked).  bfloat16 engines send every
@@ -320,6 +329,10 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
   const StepMeta hm = carve_meta(const_cast<uint8_t*>(hostm), T, B, R, max_blocks, nullptr);
   bool decode_only = true;
   for (int i = 0; i < B; ++i) decode_only &= hm.qsl[i + 1] - hm.qsl[i] == 1;
+  // Steps that carry prompt pieces run their kernels in plain stream order: they are tens of milliseconds long, early
+  // launch buys nothing there, and hundreds of long-running CTAs of one kernel waiting on the previous one would only
+  // hold shared memory.  Decode steps keep programmatic dependent launch (and run as CUDA graphs).
+  struct PdlOff { bool on; explicit PdlOff(bool o) : on(o) { if (on) pdl_suspend(true); } ~PdlOff() { if (on) pdl_suspend(false); } } pdl_off(!decode_only);
   HFWD(C_EMBED, Td * (es + 4), 0, embed_f32(e->res32, m.ids, e->embed, T, d, elt, st));
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
