@@ -280,6 +280,149 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_cols_kernel(MlstmArgs a) {
   }
 }
 
+// Prompts: the same recurrence evaluated 32 tokens at a time (chunkwise form), all in fp32.  With b_t the running sum of
+// the log forget gates inside the chunk and (C, n, m) the state before it,
+//   m_t = max(b_t + m, max_{s<=t}(b_t - b_s + i_s))                     (equal to the step-by-step maximum)
+//   num_t = e^(b_t + m - m_t) C^T q_t + sum_{s<=t} e^(b_t - b_s + i_s - m_t) (q_t . k_s) v_s
+//   n_t . q_t likewise with n and the same weights;   C' = e^(b_L + m - m_L) C + sum_s e^(b_L - b_s + i_s - m_L) k_s v_s^T
+// so a token costs the same multiply-adds as one recurrence step but the 32 tokens of a chunk are independent: no
+// barrier and no dependent chain per token.  A thread still owns one value column of C in registers.
+constexpr int ML_CH = 32, ML_NSL = 4, ML_DS = ML_MAXD / ML_NSL;      // tokens per chunk; key-dimension slices per column; dims per slice
+
+// Block = 64 value columns x 4 slices of the key dimension (256 threads): a thread keeps C[its 32 dims][its column] in
+// registers, so the read-out and the update of a chunk are spread over eight warps; the slices' partial read-outs meet in
+// shared memory and are summed in slice order.
+template <typename E>
+__global__ void __launch_bounds__(ML_COLS * ML_NSL) mlstm_chunk_kernel(MlstmArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float csm[];
+  constexpr int NT = ML_COLS * ML_NSL;
+  const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, ct = tid % ML_COLS, sl = tid / ML_COLS, c = blockIdx.z * ML_COLS + ct;
+  const int dim = a.dim, vdim = a.vdim, d0 = sl * ML_DS;
+  float* qs = csm;                           // [ML_CH][dim]   q_t * q_scale
+  float* ks = qs + ML_CH * dim;              // [ML_CH][dim]   k_s, later u_s * k_s
+  float* Sw = ks + ML_CH * dim;              // [ML_CH][ML_CH] weighted scores (s <= t)
+  float* nv = Sw + ML_CH * ML_CH;            // [ML_MAXD]
+  float* li = nv + ML_MAXD;                  // [ML_CH] log input gate
+  float* bc = li + ML_CH;                    // [ML_CH] running sum of log forget gates
+  float* mt = bc + ML_CH;                    // [ML_CH] running maximum
+  float* nq = mt + ML_CH;                    // [ML_CH] n . q_t (state part)
+  float* us = nq + ML_CH;                    // [ML_CH] weight of token s in the state after the chunk
+  float* vs = us + ML_CH;                    // [ML_CH][ML_COLS] this block's value columns of the chunk's tokens
+  float* part = vs + ML_CH * ML_COLS;        // [ML_NSL][ML_CH][ML_COLS] partial read-outs of the slices
+  const bool col = c < vdim;
+  const int rs = a.qsl[b], re = a.qsl[b + 1], p0 = a.positions[rs];
+  float* slot = a.state + (int64_t)a.slots[b] * a.slot_stride + (int64_t)h * ((int64_t)dim * vdim + dim + 1);
+  const bool fresh = p0 == 0;
+  float C[ML_DS];
+#pragma unroll
+  for (int d = 0; d < ML_DS; ++d) C[d] = (d0 + d < dim && col && !fresh) ? slot[(int64_t)(d0 + d) * vdim + c] : 0.f;
+  for (int d = tid; d < ML_MAXD; d += NT) nv[d] = (d < dim && !fresh) ? slot[(int64_t)dim * vdim + d] : 0.f;
+  float m = fresh ? 0.f : slot[(int64_t)dim * vdim + dim];
+  const E *qp = (const E*)a.q, *kp = (const E*)a.k, *vp = (const E*)a.v;
+  for (int t0 = rs; t0 < re; t0 += ML_CH) {
+    const int L = min(ML_CH, re - t0);
+    __syncthreads();                                         // the previous chunk's shared arrays are no longer read
+    for (int i = tid; i < L * dim; i += NT) {
+      const int t = i / dim, d = i % dim;
+      qs[i] = ldf(qp + (int64_t)(t0 + t) * a.ld + h * dim + d) * a.q_scale;
+      ks[i] = ldf(kp + (int64_t)(t0 + t) * a.ld + h * dim + d);
+    }
+    for (int i = tid; i < L * ML_COLS; i += NT) {
+      const int s2 = i / ML_COLS, cc = blockIdx.z * ML_COLS + i % ML_COLS;
+      vs[i] = cc < vdim ? ldf(vp + (int64_t)(t0 + s2) * a.ld + h * vdim + cc) : 0.f;
+    }
+    if (tid == 0) {                                          // the chunk's gate scalars: 32 short steps
+      float run = 0.f, mm = m;
+      for (int t = 0; t < L; ++t) {
+        const float it = a.gates[(int64_t)(t0 + t) * 2 * a.H + h], ft = a.gates[(int64_t)(t0 + t) * 2 * a.H + a.H + h];
+        mm = fmaxf(ft + mm, it);
+        run += ft;
+        li[t] = it; bc[t] = run; mt[t] = mm;
+      }
+    }
+    __syncthreads();
+    const float bL = bc[L - 1], mL = mt[L - 1];
+    // weighted scores Sw[t][s] = e^(b_t - b_s + i_s - m_t) (q_t . k_s) for s <= t; the state part of n . q_t; the tokens' weights in the new state
+    for (int i = tid; i < L * L; i += NT) {
+      const int t = i / L, s2 = i % L;
+      float w = 0.f;
+      if (s2 <= t) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (int d4 = 0; d4 < dim / 4; ++d4) {
+          const float4 q4 = reinterpret_cast<const float4*>(qs + t * dim)[d4], k4 = reinterpret_cast<const float4*>(ks + s2 * dim)[d4];
+          a0 = fmaf(q4.x, k4.x, a0); a1 = fmaf(q4.y, k4.y, a1); a2 = fmaf(q4.z, k4.z, a2); a3 = fmaf(q4.w, k4.w, a3);
+        }
+        w = expf(bc[t] - bc[s2] + li[s2] - mt[t]) * ((a0 + a1) + (a2 + a3));
+      }
+      Sw[t * ML_CH + s2] = w;
+    }
+    if (tid < L) {
+      float acc = 0.f;
+      for (int d = 0; d < dim; ++d) acc = fmaf(nv[d], qs[tid * dim + d], acc);
+      nq[tid] = acc;
+      us[tid] = expf(bL - bc[tid] + li[tid] - mL);
+    }
+    // this slice's part of C^T q_t for every token of the chunk
+    for (int t = 0; t < L; ++t) {
+      float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f;
+#pragma unroll
+      for (int d4 = 0; d4 < ML_DS / 4; ++d4) {
+        if (d0 + d4 * 4 < dim) {
+          const float4 q4 = reinterpret_cast<const float4*>(qs + t * dim + d0)[d4];
+          n0 = fmaf(C[d4 * 4 + 0], q4.x, n0); n1 = fmaf(C[d4 * 4 + 1], q4.y, n1);
+          n2 = fmaf(C[d4 * 4 + 2], q4.z, n2); n3 = fmaf(C[d4 * 4 + 3], q4.w, n3);
+        }
+      }
+      part[(sl * ML_CH + t) * ML_COLS + ct] = (n0 + n1) + (n2 + n3);
+    }
+    __syncthreads();
+    // tokens t = sl, sl + 4, ...: slices summed in order, the chunk's own tokens added, normaliser, out
+    for (int t = sl; t < L; t += ML_NSL) {
+      float inter = 0.f;
+#pragma unroll
+      for (int k = 0; k < ML_NSL; ++k) inter += part[(k * ML_CH + t) * ML_COLS + ct];
+      float intra = 0.f, rowsum = 0.f;
+      for (int s2 = 0; s2 <= t; ++s2) { const float w = Sw[t * ML_CH + s2]; intra = fmaf(w, vs[s2 * ML_COLS + ct], intra); rowsum += w; }
+      const float g = expf(bc[t] + m - mt[t]);
+      const float num = fmaf(g, inter, intra);
+      const float den = fmaxf(fabsf(fmaf(g, nq[t], rowsum)), expf(-mt[t])) + a.den_eps;
+      if (col) a.o_scratch[(int64_t)(t0 + t) * a.H * vdim + h * vdim + c] = num / den;
+    }
+    // state after the chunk: C' = G C + sum_s u_s k_s v_s^T with G = e^(b_L + m - m_L); n likewise
+    const float G = expf(bL + m - mL);
+#pragma unroll
+    for (int d = 0; d < ML_DS; ++d) C[d] *= G;
+    for (int s2 = 0; s2 < L; ++s2) {
+      const float x = us[s2] * vs[s2 * ML_COLS + ct];
+#pragma unroll
+      for (int d4 = 0; d4 < ML_DS / 4; ++d4) {
+        if (d0 + d4 * 4 < dim) {
+          const float4 k4 = reinterpret_cast<const float4*>(ks + s2 * dim + d0)[d4];
+          C[d4 * 4 + 0] = fmaf(k4.x, x, C[d4 * 4 + 0]); C[d4 * 4 + 1] = fmaf(k4.y, x, C[d4 * 4 + 1]);
+          C[d4 * 4 + 2] = fmaf(k4.z, x, C[d4 * 4 + 2]); C[d4 * 4 + 3] = fmaf(k4.w, x, C[d4 * 4 + 3]);
+        }
+      }
+    }
+    if (tid < dim) {
+      float acc = G * nv[tid];
+      for (int s2 = 0; s2 < L; ++s2) acc = fmaf(us[s2], ks[s2 * dim + tid], acc);
+      nv[tid] = acc;
+    }
+    m = mL;
+  }
+  __syncthreads();
+  if (col) {
+#pragma unroll
+    for (int d = 0; d < ML_DS; ++d) if (d0 + d < dim) slot[(int64_t)(d0 + d) * vdim + c] = C[d];
+  }
+  if (blockIdx.z == 0) {
+    for (int d = tid; d < dim; d += NT) slot[(int64_t)dim * vdim + d] = nv[d];
+    if (tid == 0) slot[(int64_t)dim * vdim + dim] = m;
+  }
+}
+
 template <typename E>
 __global__ void mlstm_norm_gate_kernel(MlstmArgs a) {
   pdl_launch_dependents();
@@ -303,6 +446,21 @@ int mlstm_step(const MlstmArgs& a, cudaStream_t st) {
     const dim3 grid(a.B, a.H, (a.vdim + ML_COLS - 1) / ML_COLS), g2(a.T, a.H);
     const int nt = std::min(256, (a.vdim + 31) / 32 * 32);
     KGE_CUDA_OK(launch_pdl(mlstm_log_gates_kernel, dim3((a.T * 2 * a.H + 255) / 256), dim3(256), 0, st, const_cast<float*>(a.gates), a.T, a.H, a.cap));
+    const size_t csm_bytes = ((size_t)2 * ML_CH * a.dim + ML_CH * ML_CH + ML_MAXD + 5 * ML_CH + (1 + ML_NSL) * ML_CH * ML_COLS) * 4;
+    if (a.T > a.B) {
+      // some request brings several rows: 32 tokens at a time (single-token requests of the same step are chunks of one)
+      static bool smem_set = false;
+      if (!smem_set) {
+        KGE_CUDA_OK(cudaFuncSetAttribute(mlstm_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        KGE_CUDA_OK(cudaFuncSetAttribute(mlstm_chunk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        smem_set = true;
+      }
+      if (a.elt == KGE_ELT_F32) KGE_CUDA_OK(launch_pdl(mlstm_chunk_kernel<float>, grid, dim3(ML_COLS * ML_NSL), csm_bytes, st, a));
+      else KGE_CUDA_OK(launch_pdl(mlstm_chunk_kernel<__nv_bfloat16>, grid, dim3(ML_COLS * ML_NSL), csm_bytes, st, a));
+      if (a.elt == KGE_ELT_F32) KGE_CUDA_OK(launch_pdl(mlstm_norm_gate_kernel<float>, g2, dim3(nt), 0, st, a));
+      else KGE_CUDA_OK(launch_pdl(mlstm_norm_gate_kernel<__nv_bfloat16>, g2, dim3(nt), 0, st, a));
+      return 0;
+    }
     if (a.elt == KGE_ELT_F32) {
       KGE_CUDA_OK(launch_pdl(mlstm_cols_kernel<float>, grid, dim3(ML_THREADS), 0, st, a));
       KGE_CUDA_OK(launch_pdl(mlstm_norm_gate_kernel<float>, g2, dim3(nt), 0, st, a));
