@@ -510,6 +510,7 @@ extern "C" void kge_engine_destroy(kge_engine* e) {
   if (e->lp_ids_host) cudaFreeHost(e->lp_ids_host);
   if (e->lp_rank_host) cudaFreeHost(e->lp_rank_host);
   if (e->mask_pairs_host) cudaFreeHost(e->mask_pairs_host);
+  if (e->moe_goff_host) cudaFreeHost(e->moe_goff_host);
   if (e->stream) cudaStreamDestroy(e->stream);
   delete e;
 }

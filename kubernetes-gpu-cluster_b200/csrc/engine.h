@@ -91,7 +91,8 @@ struct kge_engine {
   std::vector<kge::HybridLayerW> hyb;
   float *res32 = nullptr, *gates32 = nullptr, *logits32 = nullptr, *state = nullptr, *mo32 = nullptr;
   void *hx = nullptr, *pbuf = nullptr, *ubuf = nullptr, *mixbuf = nullptr, *obuf1 = nullptr, *obuf2 = nullptr, *ffbuf = nullptr;
-  void *moe_hidden = nullptr, *moe_out = nullptr, *hsel = nullptr;
+  void *moe_hidden = nullptr, *moe_out = nullptr, *hsel = nullptr, *moe_xperm = nullptr, *moe_operm = nullptr;
+  int32_t* moe_goff_host = nullptr;          // pinned copy of the experts' row offsets (prompt steps size one GEMM per expert from it)
   int32_t *moe_goff = nullptr, *moe_ptok = nullptr, *moe_pdest = nullptr, *moe_cexp = nullptr;
   float *moe_pw = nullptr, *moe_cw = nullptr;
   int64_t slot_stride = 0;                   // floats per state slot

@@ -167,11 +167,12 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
     } else if (h.mlp == HybridLayerSpec::MOE) {
       L.router.N = h.experts; L.router.K = d;
       HB_OK(L.router.w = b.mat({fp + "router"}, {h.experts}, d, ws * 4));
-      std::vector<std::string> g, u, dn;
-      std::vector<int64_t> lf((size_t)h.experts, h.expert_ff), ld((size_t)h.experts, d);
-      for (int x = 0; x < h.experts; ++x) { const std::string ep = fp + "e" + std::to_string(x) + "."; g.push_back(ep + "gate"); u.push_back(ep + "up"); dn.push_back(ep + "down"); }
-      HB_OK(L.e_gate = b.mat(g, lf, d, ws));
-      HB_OK(L.e_up = b.mat(u, lf, d, ws));
+      // per expert [gate | up] rows in one block (what the fused gated GEMM reads), then all experts' down matrices
+      std::vector<std::string> gu, dn;
+      std::vector<int64_t> lf((size_t)2 * h.experts, h.expert_ff), ld((size_t)h.experts, d);
+      for (int x = 0; x < h.experts; ++x) { const std::string ep = fp + "e" + std::to_string(x) + "."; gu.push_back(ep + "gate"); gu.push_back(ep + "up"); dn.push_back(ep + "down"); }
+      HB_OK(L.e_gate = b.mat(gu, lf, d, ws));
+      L.e_up = (uint8_t*)L.e_gate + (int64_t)h.expert_ff * d * b.esz();
       HB_OK(L.e_down = b.mat(dn, ld, h.expert_ff, ws));
       if (h.shared_ff > 0) {
         L.s_gate.N = L.s_up.N = h.shared_ff; L.s_gate.K = L.s_up.K = d; L.s_down.N = d; L.s_down.K = h.shared_ff;
@@ -213,6 +214,10 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
     const int64_t np = (int64_t)Tm * max_top;
     e->moe_hidden = aalloc(np * max_eff, es);
     e->moe_out = aalloc(np * d, es);
+    if (!e->f32) {
+      e->moe_xperm = aalloc(np * d, 2); e->moe_operm = aalloc(np * d, 2);
+      if (!e->moe_xperm || !e->moe_operm || cudaMallocHost((void**)&e->moe_goff_host, (size_t)(max_E + 1) * 4) != cudaSuccess) return fail("expert staging allocation failed: " + b.err);
+    }
     e->moe_goff = (int32_t*)aalloc(max_E + 1, 4);
     e->moe_ptok = (int32_t*)aalloc(np, 4); e->moe_pdest = (int32_t*)aalloc(np, 4); e->moe_cexp = (int32_t*)aalloc(np, 4);
     e->moe_pw = (float*)aalloc(np, 4); e->moe_cw = (float*)aalloc(np, 4);
@@ -409,9 +414,29 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       ++e->launches;
       const int np = T * h.top;
       const double wexp = (double)std::min(h.experts, np) * h.expert_ff * d * es;      // weights of the experts that are touched (at most)
+      if (!e->f32 && !decode_only && np >= 512 && h.expert_ff % 64 == 0 && d % 8 == 0 && e->moe_xperm) {
+        // prompt steps: the routed rows are made contiguous per expert and every expert runs the tensor-core GEMMs
+        // (gated front half with SiLU*mul in the epilogue, then down) on its own rows; the row counts come to the host
+        // once per layer - a few microseconds beside milliseconds of expert work
+        const int eff = h.expert_ff;
+        HFWD(C_MOE, (double)np * d * 4, 0, moe_gather_rows(e->moe_xperm, e->hx, d, e->moe_ptok, e->moe_pw, np, d, st));
+        KGE_CUDA_OK(cudaMemcpyAsync(e->moe_goff_host, e->moe_goff, (size_t)(h.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
+        KGE_CUDA_OK(cudaStreamSynchronize(st));
+        for (int x = 0; x < h.experts; ++x) {
+          const int off = e->moe_goff_host[x], cnt = e->moe_goff_host[x + 1] - off;
+          if (cnt <= 0) continue;
+          const uint8_t* wgu = (const uint8_t*)L.e_gate + (int64_t)x * 2 * eff * d * 2;
+          const uint8_t* wdn = (const uint8_t*)L.e_down + (int64_t)x * d * eff * 2;
+          HFWD(cnt <= 256 ? C_GEMM_S : C_MOE, 2.0 * (2.0 * eff * d + (double)cnt * (d + eff)), 4.0 * cnt * (double)eff * d,
+               kge_gemm_silu_gate_ws_bf16(at(e->moe_hidden, (int64_t)off * eff), at(e->moe_xperm, (int64_t)off * d), wgu, cnt, eff, d, nullptr, 0, st));
+          HFWD(cnt <= 256 ? C_GEMM_S : C_MOE, 2.0 * ((double)eff * d + (double)cnt * (d + eff)), 2.0 * cnt * (double)eff * d,
+               kge_gemm_bf16(at(e->moe_operm, (int64_t)off * d), at(e->moe_hidden, (int64_t)off * eff), wdn, nullptr, cnt, d, eff, 0, nullptr, 0, st));
+        }
+        HFWD(C_MOE, (double)np * d * 4, 0, moe_scatter_rows(e->moe_out, e->moe_operm, e->moe_pdest, np, d, st));
+      } else {
       LinearArgs g;      // experts' gated front half on the gathered, weighted rows
       g.x = e->hx; g.ldx = d; g.w = L.e_gate; g.w2 = L.e_up; g.y = e->moe_hidden; g.ldy = h.expert_ff; g.T = np; g.N = h.expert_ff; g.K = d;
-      g.nz = h.experts; g.w_zs = (int64_t)h.expert_ff * d; g.group_off = e->moe_goff; g.max_rows = np; g.xrows = e->moe_ptok; g.row_scale = e->moe_pw;
+      g.nz = h.experts; g.w_zs = (int64_t)2 * h.expert_ff * d; g.group_off = e->moe_goff; g.max_rows = np; g.xrows = e->moe_ptok; g.row_scale = e->moe_pw;
       g.elt = elt; g.out_f32 = e->f32;
       HFWD(C_MOE, 2 * wexp + (double)np * (d + h.expert_ff) * es, 4.0 * np * (double)h.expert_ff * d, linear_any(g, st));
       LinearArgs dn;     // experts' down projection, scattered to row (token * top + choice)
@@ -419,6 +444,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       dn.nz = h.experts; dn.w_zs = (int64_t)d * h.expert_ff; dn.group_off = e->moe_goff; dn.max_rows = np; dn.yrows = e->moe_pdest;
       dn.elt = elt; dn.out_f32 = e->f32;
       HFWD(C_MOE, wexp + (double)np * (d + h.expert_ff) * es, 2.0 * np * (double)h.expert_ff * d, linear_any(dn, st));
+      }
       if (h.shared_ff > 0) {
         const int f = h.shared_ff;
         const double gb = es * (2.0 * f * d + (double)T * (d + f)), gf = 4.0 * T * (double)f * d;

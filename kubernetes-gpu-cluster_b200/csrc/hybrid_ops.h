@@ -126,5 +126,8 @@ struct MoeRouteArgs {
   int elt = KGE_ELT_BF16;
 };
 int moe_route(const MoeRouteArgs& a, cudaStream_t st);
+// routed rows made contiguous per expert: xperm[p, :] = bf16(perm_weight[p] * h[perm_token[p], :]); and back: out[perm_dest[p], :] = operm[p, :]
+int moe_gather_rows(void* xperm, const void* h, int ldh, const int32_t* perm_token, const float* perm_weight, int np, int d, cudaStream_t st);
+int moe_scatter_rows(void* out, const void* operm, const int32_t* perm_dest, int np, int d, cudaStream_t st);
 
 }  // namespace kge

@@ -80,6 +80,31 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(MoeRouteArgs a) {
   }
 }
 
+__global__ void moe_gather_rows_kernel(__nv_bfloat16* xperm, const __nv_bfloat16* h, int ldh, const int32_t* tok, const float* w, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int p = blockIdx.x;
+  const __nv_bfloat16* src = h + (int64_t)tok[p] * ldh;
+  const float s = w[p];
+  for (int c = threadIdx.x; c < d; c += blockDim.x) xperm[(int64_t)p * d + c] = __float2bfloat16_rn(s * __bfloat162float(src[c]));
+}
+__global__ void moe_scatter_rows_kernel(__nv_bfloat16* out, const __nv_bfloat16* operm, const int32_t* dest, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int p = blockIdx.x;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) out[(int64_t)dest[p] * d + c] = operm[(int64_t)p * d + c];
+}
+int moe_gather_rows(void* xperm, const void* h, int ldh, const int32_t* perm_token, const float* perm_weight, int np, int d, cudaStream_t st) {
+  if (np <= 0) return 0;
+  KGE_CUDA_OK(launch_pdl(moe_gather_rows_kernel, dim3(np), dim3(256), 0, st, (__nv_bfloat16*)xperm, (const __nv_bfloat16*)h, ldh, perm_token, perm_weight, d));
+  return 0;
+}
+int moe_scatter_rows(void* out, const void* operm, const int32_t* perm_dest, int np, int d, cudaStream_t st) {
+  if (np <= 0) return 0;
+  KGE_CUDA_OK(launch_pdl(moe_scatter_rows_kernel, dim3(np), dim3(256), 0, st, (__nv_bfloat16*)out, (const __nv_bfloat16*)operm, perm_dest, d));
+  return 0;
+}
+
 int moe_route(const MoeRouteArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
   KGE_REQUIRE(a.E > 0 && a.top > 0 && a.top <= a.E && a.E <= 4096, "moe_route: %d experts, top %d", a.E, a.top);

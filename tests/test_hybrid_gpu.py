@@ -201,6 +201,20 @@ def test_far_keys_among_hundreds(kge, tmp_path):
     check(got, want, "float32")
 
 
+def test_experts_with_many_routed_rows(kge, tmp_path):
+    """A prompt long enough that the routed rows are made contiguous per expert and run as one tensor-core GEMM pair per
+    expert (bfloat16; expert width a multiple of 64); the same prompt fed in short pieces takes the grouped kernel."""
+    cfg = oh.make_config(layers=("rglru",), mlps=("moe",), experts=6, top=2, expert_ff=64, shared_ff=64, r_width=64, r_blocks=2)
+    W = oh.make_weights(cfg, seed=16)
+    toks = prompt(cfg, 300, 33)
+    want = oh.forward(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", bs=64)
+    check(run_pieces(llm, 0, toks, [300]), want, "bfloat16", "one step")
+    llm.trace_end(0)
+    check(run_pieces(llm, 1, toks, [280, 7, 13]), want, "bfloat16", "pieces")
+    llm.close()
+
+
 def test_first_tokens(kge, tmp_path):
     cfg = oh.make_config(**FULL)
     W = oh.make_weights(cfg, seed=11)
