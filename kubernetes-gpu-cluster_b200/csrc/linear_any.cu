@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(256) linear_any_kernel(LinearArgs a) {
 // bfloat16 operands: the same tiling on the tensor cores (mma.sync m16n8k16, fp32 accumulators).  Both operands are
 // k-contiguous, which is exactly the row x col fragment layout, so the fragments are 32-bit loads from k-padded shared
 // tiles.  Eight warps as 2 x 4, each 32 rows x 16 outputs; a row's sum is formed in the same k order whatever the launch holds.
-constexpr int MBK = 32, MPAD = 8;
+constexpr int MPAD = 8;       // the k-tile is 32 wide for many rows and 64 for few (weight streaming: fewer, fatter round trips)
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -118,7 +118,7 @@ __device__ __forceinline__ uint4 load8(const __nv_bfloat16* row, int k, int K, b
   return u.v;
 }
 
-template <typename O, bool DUAL>
+template <typename O, bool DUAL, int MBK>
 __global__ void __launch_bounds__(256) linear_mma_kernel(LinearArgs a) {
   pdl_launch_dependents();
   pdl_wait();
@@ -147,17 +147,29 @@ __global__ void __launch_bounds__(256) linear_mma_kernel(LinearArgs a) {
   const bool wvec = ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && a.K % 8 == 0 && (!DUAL || (reinterpret_cast<uintptr_t>(w2) & 15) == 0);
   float acc[2][2][4] = {}, acc2[DUAL ? 2 : 1][2][4] = {};
   // the next k-tile travels from global memory to registers while the tensor cores work on the current one
-  uint4 px = load8(xrow, sk, a.K, xvec), pw = load8(wrow, sk, a.K, wvec), pw2 = make_uint4(0u, 0u, 0u, 0u);
-  if (DUAL) pw2 = load8(w2row, sk, a.K, wvec);
+  constexpr int NU = MBK / 32;                 // 16-byte pieces per thread, operand and k-tile
+  uint4 px[NU], pw[NU], pw2[NU];
+#pragma unroll
+  for (int u = 0; u < NU; ++u) {
+    px[u] = load8(xrow, sk + u * 32, a.K, xvec);
+    pw[u] = load8(wrow, sk + u * 32, a.K, wvec);
+    pw2[u] = DUAL ? load8(w2row, sk + u * 32, a.K, wvec) : make_uint4(0u, 0u, 0u, 0u);
+  }
   for (int k0 = 0; k0 < a.K; k0 += MBK) {
-    *reinterpret_cast<uint4*>(&xs[sr][sk]) = px;
-    *reinterpret_cast<uint4*>(&ws[sr][sk]) = pw;
-    if (DUAL) *reinterpret_cast<uint4*>(&ws2[sr][sk]) = pw2;
+#pragma unroll
+    for (int u = 0; u < NU; ++u) {
+      *reinterpret_cast<uint4*>(&xs[sr][sk + u * 32]) = px[u];
+      *reinterpret_cast<uint4*>(&ws[sr][sk + u * 32]) = pw[u];
+      if (DUAL) *reinterpret_cast<uint4*>(&ws2[sr][sk + u * 32]) = pw2[u];
+    }
     __syncthreads();
     if (k0 + MBK < a.K) {
-      px = load8(xrow, k0 + MBK + sk, a.K, xvec);
-      pw = load8(wrow, k0 + MBK + sk, a.K, wvec);
-      if (DUAL) pw2 = load8(w2row, k0 + MBK + sk, a.K, wvec);
+#pragma unroll
+      for (int u = 0; u < NU; ++u) {
+        px[u] = load8(xrow, k0 + MBK + sk + u * 32, a.K, xvec);
+        pw[u] = load8(wrow, k0 + MBK + sk + u * 32, a.K, wvec);
+        if (DUAL) pw2[u] = load8(w2row, k0 + MBK + sk + u * 32, a.K, wvec);
+      }
     }
 #pragma unroll
     for (int ks = 0; ks < MBK / 16; ++ks) {
@@ -222,8 +234,11 @@ int linear_any(const LinearArgs& a, cudaStream_t st) {
   const bool f32 = a.elt == KGE_ELT_F32;
   KGE_REQUIRE(!f32 || a.out_f32, "linear_any: float32 storage writes float32");
   if (f32) ce = a.w2 ? launch_pdl(linear_any_kernel<float, float, true>, grid, block, 0, st, a) : launch_pdl(linear_any_kernel<float, float, false>, grid, block, 0, st, a);
-  else if (a.out_f32) ce = a.w2 ? launch_pdl(linear_mma_kernel<float, true>, grid, block, 0, st, a) : launch_pdl(linear_mma_kernel<float, false>, grid, block, 0, st, a);
-  else ce = a.w2 ? launch_pdl(linear_mma_kernel<__nv_bfloat16, true>, grid, block, 0, st, a) : launch_pdl(linear_mma_kernel<__nv_bfloat16, false>, grid, block, 0, st, a);
+  else if (a.T <= 256) {       // few rows: the weights are the traffic
+    if (a.out_f32) ce = a.w2 ? launch_pdl(linear_mma_kernel<float, true, 64>, grid, block, 0, st, a) : launch_pdl(linear_mma_kernel<float, false, 64>, grid, block, 0, st, a);
+    else ce = a.w2 ? launch_pdl(linear_mma_kernel<__nv_bfloat16, true, 64>, grid, block, 0, st, a) : launch_pdl(linear_mma_kernel<__nv_bfloat16, false, 64>, grid, block, 0, st, a);
+  } else if (a.out_f32) ce = a.w2 ? launch_pdl(linear_mma_kernel<float, true, 32>, grid, block, 0, st, a) : launch_pdl(linear_mma_kernel<float, false, 32>, grid, block, 0, st, a);
+  else ce = a.w2 ? launch_pdl(linear_mma_kernel<__nv_bfloat16, true, 32>, grid, block, 0, st, a) : launch_pdl(linear_mma_kernel<__nv_bfloat16, false, 32>, grid, block, 0, st, a);
   KGE_CUDA_OK(ce);
   return 0;
 }
