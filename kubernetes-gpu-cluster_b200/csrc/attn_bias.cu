@@ -167,21 +167,35 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
     const int jl = j0 + lane;
     const int64_t myrow = jl <= pos_last ? ((int64_t)bt[jl / a.block_size] * a.G + g) * a.block_size + jl % a.block_size : -1;
     const int sid = ROWS ? threadIdx.x : lane, sstep = ROWS ? AM_WARPS * 32 : 32;
-    for (int idx0 = 0; idx0 < AM_KT * kseg; idx0 += sstep) {       // whole warps run the loop: the shuffle needs every lane
-      const int idx = min(idx0 + sid, AM_KT * kseg - 1);
-      const int key = idx / kseg, seg = idx % kseg;
-      const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row >= 0) v = *reinterpret_cast<const uint4*>(kc + row * dim + seg * 8);
-      *reinterpret_cast<uint4*>(Ks + key * kst + seg * 8) = v;
+    // four 16-byte pieces are requested before the first is stored, so a tile costs a few memory round trips, not one
+    // per piece (whole warps run the loops: the shuffle needs every lane)
+    for (int idx0 = 0; idx0 < AM_KT * kseg; idx0 += 4 * sstep) {
+      uint4 v[4]; int dst[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = min(idx0 + u * sstep + sid, AM_KT * kseg - 1);
+        const int key = idx / kseg, seg = idx % kseg;
+        const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (row >= 0) v[u] = *reinterpret_cast<const uint4*>(kc + row * dim + seg * 8);
+        dst[u] = key * kst + seg * 8;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(Ks + dst[u]) = v[u];
     }
-    for (int idx0 = 0; idx0 < AM_KT * vseg; idx0 += sstep) {
-      const int idx = min(idx0 + sid, AM_KT * vseg - 1);
-      const int key = idx / vseg, seg = idx % vseg;
-      const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row >= 0) v = *reinterpret_cast<const uint4*>(vc + row * vdim + seg * 8);
-      *reinterpret_cast<uint4*>(Vs + key * vst + seg * 8) = v;
+    for (int idx0 = 0; idx0 < AM_KT * vseg; idx0 += 4 * sstep) {
+      uint4 v[4]; int dst[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = min(idx0 + u * sstep + sid, AM_KT * vseg - 1);
+        const int key = idx / vseg, seg = idx % vseg;
+        const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (row >= 0) v[u] = *reinterpret_cast<const uint4*>(vc + row * vdim + seg * 8);
+        dst[u] = key * vst + seg * 8;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(Vs + dst[u]) = v[u];
     }
     if (ROWS) __syncthreads(); else __syncwarp();
     if (ROWS && (j0 > own_hi || j0 + AM_KT <= own_lo)) continue;
