@@ -8,24 +8,25 @@
 
 namespace kge {
 
+// One block per token: its eight warps share the experts' dot products (fp32, ascending d per lane, lanes summed by
+// shuffles - the same order whatever the launch holds), then one thread picks the top-k.
 template <typename E>
-__global__ void __launch_bounds__(128) moe_score_kernel(MoeRouteArgs a) {
+__global__ void __launch_bounds__(256) moe_score_kernel(MoeRouteArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float sc_all[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= a.T) return;
-  float* sc = sc_all + warp * a.E;
+  extern __shared__ float sc[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x;
   const E* h = (const E*)a.h + (int64_t)t * a.ldh;
-  for (int e = 0; e < a.E; ++e) {
+  for (int e = warp; e < a.E; e += 8) {
     const E* w = (const E*)a.w_router + (int64_t)e * a.d;
     float acc = 0.f;
+#pragma unroll 8
     for (int k = lane; k < a.d; k += 32) acc = fmaf(ldf(h + k), ldf(w + k), acc);
     acc = warp_sum(acc);
     if (lane == 0) sc[e] = acc;
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   if (a.score_fn == 0) {
     for (int e = lane; e < a.E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
   } else {
@@ -48,6 +49,7 @@ __global__ void __launch_bounds__(128) moe_score_kernel(MoeRouteArgs a) {
         for (int q = 0; q < k; ++q) taken |= a.choice_expert[(int64_t)t * a.top + q] == e;
         if (!taken && sc[e] > bv) { bv = sc[e]; best = e; }
       }
+      if (best < 0) { best = 0; for (int q = 0; q < k; ++q) if (a.choice_expert[(int64_t)t * a.top + q] == best) ++best; bv = 0.f; }   // scores that are not numbers
       a.choice_expert[(int64_t)t * a.top + k] = best;
       a.choice_weight[(int64_t)t * a.top + k] = bv;
       total += bv;
@@ -108,8 +110,8 @@ int moe_scatter_rows(void* out, const void* operm, const int32_t* perm_dest, int
 int moe_route(const MoeRouteArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
   KGE_REQUIRE(a.E > 0 && a.top > 0 && a.top <= a.E && a.E <= 4096, "moe_route: %d experts, top %d", a.E, a.top);
-  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(moe_score_kernel<float>, dim3((a.T + 3) / 4), dim3(128), (size_t)4 * a.E * 4, st, a)
-                                        : launch_pdl(moe_score_kernel<__nv_bfloat16>, dim3((a.T + 3) / 4), dim3(128), (size_t)4 * a.E * 4, st, a);
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(moe_score_kernel<float>, dim3(a.T), dim3(256), (size_t)a.E * 4, st, a)
+                                        : launch_pdl(moe_score_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), (size_t)a.E * 4, st, a);
   KGE_CUDA_OK(ce);
   KGE_CUDA_OK(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)2 * a.E * 4, st, a));
   return 0;
