@@ -108,10 +108,100 @@ __global__ void __launch_bounds__(128) rglru_scan_kernel(RglruArgs a) {
   }
 }
 
+// Prompt steps: everything of the recurrence that does not depend on the previous token is done for all tokens at once.
+// rglru_ab_kernel turns the gate pre-activations, in place, into the recurrence's coefficients (a_t, b_t = sqrt(1 - a_t^2)
+// i_t u_t); rglru_chain_kernel is then one fma per token and channel (S_t written over a_t) plus the state hand-over; and
+// rglru_out_kernel multiplies by gelu(y).  Same arithmetic per element as the fused kernel.
+template <typename E>
+__global__ void rglru_ab_kernel(RglruArgs a, float* gates) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t n = (int64_t)a.T * a.width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / a.width; const int c = (int)(i % a.width);
+    const float sp = a.decay_c * softplusf_(ldf((const E*)a.lam + c));
+    const float r = sigmoidf_(gates[t * 2 * a.width + c]), ig = sigmoidf_(gates[t * 2 * a.width + a.width + c]);
+    const float log_a = -sp * r;
+    gates[t * 2 * a.width + c] = expf(log_a);
+    gates[t * 2 * a.width + a.width + c] = sqrtf(-expm1f(2.f * log_a)) * ig * ldf((const E*)a.u + t * a.width + c);
+  }
+}
+
+template <typename E>
+__global__ void __launch_bounds__(128) rglru_chain_kernel(RglruArgs a, float* gates) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.width) return;
+  const int rs = a.qsl[b], re = a.qsl[b + 1], p0 = a.positions[rs], n = re - rs;
+  float* slot = a.state + (int64_t)a.slots[b] * a.slot_stride;
+  const E* yx = (const E*)a.yx;
+  float S = p0 > 0 ? slot[c] : 0.f;
+  constexpr int G = 8;
+  for (int t0 = rs; t0 < re; t0 += G) {
+    float av[G], bv[G];
+#pragma unroll
+    for (int k = 0; k < G; ++k) {
+      const int t = min(t0 + k, re - 1);
+      av[k] = gates[(int64_t)t * 2 * a.width + c];
+      bv[k] = gates[(int64_t)t * 2 * a.width + a.width + c];
+    }
+#pragma unroll
+    for (int k = 0; k < G; ++k) {
+      if (t0 + k < re) {
+        S = fmaf(av[k], S, bv[k]);
+        gates[(int64_t)(t0 + k) * 2 * a.width + c] = S;
+      }
+    }
+  }
+  slot[c] = S;
+  float nt[MAX_TAPS];
+  float* tail = slot + a.width;
+#pragma unroll
+  for (int k = 0; k < MAX_TAPS; ++k) {
+    if (k >= a.taps - 1) break;
+    const int sp2 = p0 + n - (a.taps - 1) + k;
+    float v = 0.f;
+    if (sp2 >= p0) v = ldf(yx + (int64_t)(rs + sp2 - p0) * 2 * a.width + a.width + c);
+    else if (sp2 >= 0) v = tail[(int64_t)(sp2 - p0 + a.taps - 1) * a.width + c];
+    nt[k] = v;
+  }
+#pragma unroll
+  for (int k = 0; k < MAX_TAPS; ++k) {
+    if (k >= a.taps - 1) break;
+    tail[(int64_t)k * a.width + c] = nt[k];
+  }
+}
+
+template <typename E>
+__global__ void rglru_out_kernel(RglruArgs a, const float* gates) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t n = (int64_t)a.T * a.width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / a.width; const int c = (int)(i % a.width);
+    stf((E*)a.out + i, gates[t * 2 * a.width + c] * gelu_tanhf_(ldf((const E*)a.yx + t * 2 * a.width + c)));
+  }
+}
+
 int rglru_scan(const RglruArgs& a, cudaStream_t st) {
   if (a.T <= 0 || a.B <= 0) return 0;
   KGE_REQUIRE(a.taps >= 1 && a.taps <= MAX_TAPS, "rglru_scan: %d taps (1..%d)", a.taps, MAX_TAPS);
   const dim3 grid(a.B, (a.width + 127) / 128), block(128);
+  if (a.T > a.B) {                       // some request brings several rows
+    float* gates = const_cast<float*>(a.gates);
+    const int eg = (int)std::min<int64_t>(((int64_t)a.T * a.width + 255) / 256, 148 * 16);
+    if (a.elt == KGE_ELT_F32) {
+      KGE_CUDA_OK(launch_pdl(rglru_ab_kernel<float>, dim3(eg), dim3(256), 0, st, a, gates));
+      KGE_CUDA_OK(launch_pdl(rglru_chain_kernel<float>, grid, block, 0, st, a, gates));
+      KGE_CUDA_OK(launch_pdl(rglru_out_kernel<float>, dim3(eg), dim3(256), 0, st, a, (const float*)gates));
+    } else {
+      KGE_CUDA_OK(launch_pdl(rglru_ab_kernel<__nv_bfloat16>, dim3(eg), dim3(256), 0, st, a, gates));
+      KGE_CUDA_OK(launch_pdl(rglru_chain_kernel<__nv_bfloat16>, grid, block, 0, st, a, gates));
+      KGE_CUDA_OK(launch_pdl(rglru_out_kernel<__nv_bfloat16>, dim3(eg), dim3(256), 0, st, a, (const float*)gates));
+    }
+    return 0;
+  }
   cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(rglru_scan_kernel<float>, grid, block, 0, st, a)
                                         : launch_pdl(rglru_scan_kernel<__nv_bfloat16>, grid, block, 0, st, a);
   KGE_CUDA_OK(ce);
@@ -288,17 +378,18 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_cols_kernel(MlstmArgs a) {
 // so a token costs the same multiply-adds as one recurrence step but the 32 tokens of a chunk are independent: no
 // barrier and no dependent chain per token.  A thread still owns one value column of C in registers.
 constexpr int ML_CH = 32, ML_NSL = 4, ML_DS = ML_MAXD / ML_NSL;      // tokens per chunk; key-dimension slices per column; dims per slice
+constexpr int MC_COLS = 32;          // value columns per block of the chunkwise kernel: more, smaller blocks fill the machine when few requests prefill
 
-// Block = 64 value columns x 4 slices of the key dimension (256 threads): a thread keeps C[its 32 dims][its column] in
-// registers, so the read-out and the update of a chunk are spread over eight warps; the slices' partial read-outs meet in
+// Block = 32 value columns x 4 slices of the key dimension (128 threads): a thread keeps C[its 32 dims][its column] in
+// registers, so the read-out and the update of a chunk are spread over four warps; the slices' partial read-outs meet in
 // shared memory and are summed in slice order.
 template <typename E>
-__global__ void __launch_bounds__(ML_COLS * ML_NSL) mlstm_chunk_kernel(MlstmArgs a) {
+__global__ void __launch_bounds__(MC_COLS * ML_NSL) mlstm_chunk_kernel(MlstmArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float csm[];
-  constexpr int NT = ML_COLS * ML_NSL;
-  const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, ct = tid % ML_COLS, sl = tid / ML_COLS, c = blockIdx.z * ML_COLS + ct;
+  constexpr int NT = MC_COLS * ML_NSL;
+  const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, ct = tid % MC_COLS, sl = tid / MC_COLS, c = blockIdx.z * MC_COLS + ct;
   const int dim = a.dim, vdim = a.vdim, d0 = sl * ML_DS;
   float* qs = csm;                           // [ML_CH][dim]   q_t * q_scale
   float* ks = qs + ML_CH * dim;              // [ML_CH][dim]   k_s, later u_s * k_s
@@ -309,8 +400,8 @@ __global__ void __launch_bounds__(ML_COLS * ML_NSL) mlstm_chunk_kernel(MlstmArgs
   float* mt = bc + ML_CH;                    // [ML_CH] running maximum
   float* nq = mt + ML_CH;                    // [ML_CH] n . q_t (state part)
   float* us = nq + ML_CH;                    // [ML_CH] weight of token s in the state after the chunk
-  float* vs = us + ML_CH;                    // [ML_CH][ML_COLS] this block's value columns of the chunk's tokens
-  float* part = vs + ML_CH * ML_COLS;        // [ML_NSL][ML_CH][ML_COLS] partial read-outs of the slices
+  float* vs = us + ML_CH;                    // [ML_CH][MC_COLS] this block's value columns of the chunk's tokens
+  float* part = vs + ML_CH * MC_COLS;        // [ML_NSL][ML_CH][MC_COLS] partial read-outs of the slices
   const bool col = c < vdim;
   const int rs = a.qsl[b], re = a.qsl[b + 1], p0 = a.positions[rs];
   float* slot = a.state + (int64_t)a.slots[b] * a.slot_stride + (int64_t)h * ((int64_t)dim * vdim + dim + 1);
@@ -329,8 +420,8 @@ __global__ void __launch_bounds__(ML_COLS * ML_NSL) mlstm_chunk_kernel(MlstmArgs
       qs[i] = ldf(qp + (int64_t)(t0 + t) * a.ld + h * dim + d) * a.q_scale;
       ks[i] = ldf(kp + (int64_t)(t0 + t) * a.ld + h * dim + d);
     }
-    for (int i = tid; i < L * ML_COLS; i += NT) {
-      const int s2 = i / ML_COLS, cc = blockIdx.z * ML_COLS + i % ML_COLS;
+    for (int i = tid; i < L * MC_COLS; i += NT) {
+      const int s2 = i / MC_COLS, cc = blockIdx.z * MC_COLS + i % MC_COLS;
       vs[i] = cc < vdim ? ldf(vp + (int64_t)(t0 + s2) * a.ld + h * vdim + cc) : 0.f;
     }
     if (tid == 0) {                                          // the chunk's gate scalars: 32 short steps
@@ -358,11 +449,11 @@ __global__ void __launch_bounds__(ML_COLS * ML_NSL) mlstm_chunk_kernel(MlstmArgs
       }
       Sw[t * ML_CH + s2] = w;
     }
-    if (tid < L) {
+    for (int t = tid; t < L; t += NT) {
       float acc = 0.f;
-      for (int d = 0; d < dim; ++d) acc = fmaf(nv[d], qs[tid * dim + d], acc);
-      nq[tid] = acc;
-      us[tid] = expf(bL - bc[tid] + li[tid] - mL);
+      for (int d = 0; d < dim; ++d) acc = fmaf(nv[d], qs[t * dim + d], acc);
+      nq[t] = acc;
+      us[t] = expf(bL - bc[t] + li[t] - mL);
     }
     // this slice's part of C^T q_t for every token of the chunk
     for (int t = 0; t < L; ++t) {
@@ -375,16 +466,16 @@ __global__ void __launch_bounds__(ML_COLS * ML_NSL) mlstm_chunk_kernel(MlstmArgs
           n2 = fmaf(C[d4 * 4 + 2], q4.z, n2); n3 = fmaf(C[d4 * 4 + 3], q4.w, n3);
         }
       }
-      part[(sl * ML_CH + t) * ML_COLS + ct] = (n0 + n1) + (n2 + n3);
+      part[(sl * ML_CH + t) * MC_COLS + ct] = (n0 + n1) + (n2 + n3);
     }
     __syncthreads();
     // tokens t = sl, sl + 4, ...: slices summed in order, the chunk's own tokens added, normaliser, out
     for (int t = sl; t < L; t += ML_NSL) {
       float inter = 0.f;
 #pragma unroll
-      for (int k = 0; k < ML_NSL; ++k) inter += part[(k * ML_CH + t) * ML_COLS + ct];
+      for (int k = 0; k < ML_NSL; ++k) inter += part[(k * ML_CH + t) * MC_COLS + ct];
       float intra = 0.f, rowsum = 0.f;
-      for (int s2 = 0; s2 <= t; ++s2) { const float w = Sw[t * ML_CH + s2]; intra = fmaf(w, vs[s2 * ML_COLS + ct], intra); rowsum += w; }
+      for (int s2 = 0; s2 <= t; ++s2) { const float w = Sw[t * ML_CH + s2]; intra = fmaf(w, vs[s2 * MC_COLS + ct], intra); rowsum += w; }
       const float g = expf(bc[t] + m - mt[t]);
       const float num = fmaf(g, inter, intra);
       const float den = fmaxf(fabsf(fmaf(g, nq[t], rowsum)), expf(-mt[t])) + a.den_eps;
@@ -395,7 +486,7 @@ __global__ void __launch_bounds__(ML_COLS * ML_NSL) mlstm_chunk_kernel(MlstmArgs
 #pragma unroll
     for (int d = 0; d < ML_DS; ++d) C[d] *= G;
     for (int s2 = 0; s2 < L; ++s2) {
-      const float x = us[s2] * vs[s2 * ML_COLS + ct];
+      const float x = us[s2] * vs[s2 * MC_COLS + ct];
 #pragma unroll
       for (int d4 = 0; d4 < ML_DS / 4; ++d4) {
         if (d0 + d4 * 4 < dim) {
@@ -405,10 +496,10 @@ __global__ void __launch_bounds__(ML_COLS * ML_NSL) mlstm_chunk_kernel(MlstmArgs
         }
       }
     }
-    if (tid < dim) {
-      float acc = G * nv[tid];
-      for (int s2 = 0; s2 < L; ++s2) acc = fmaf(us[s2], ks[s2 * dim + tid], acc);
-      nv[tid] = acc;
+    for (int d = tid; d < dim; d += NT) {
+      float acc = G * nv[d];
+      for (int s2 = 0; s2 < L; ++s2) acc = fmaf(us[s2], ks[s2 * dim + d], acc);
+      nv[d] = acc;
     }
     m = mL;
   }
@@ -446,7 +537,8 @@ int mlstm_step(const MlstmArgs& a, cudaStream_t st) {
     const dim3 grid(a.B, a.H, (a.vdim + ML_COLS - 1) / ML_COLS), g2(a.T, a.H);
     const int nt = std::min(256, (a.vdim + 31) / 32 * 32);
     KGE_CUDA_OK(launch_pdl(mlstm_log_gates_kernel, dim3((a.T * 2 * a.H + 255) / 256), dim3(256), 0, st, const_cast<float*>(a.gates), a.T, a.H, a.cap));
-    const size_t csm_bytes = ((size_t)2 * ML_CH * a.dim + ML_CH * ML_CH + ML_MAXD + 5 * ML_CH + (1 + ML_NSL) * ML_CH * ML_COLS) * 4;
+    const size_t csm_bytes = ((size_t)2 * ML_CH * a.dim + ML_CH * ML_CH + ML_MAXD + 5 * ML_CH + (1 + ML_NSL) * ML_CH * MC_COLS) * 4;
+    const dim3 cgrid(a.B, a.H, (a.vdim + MC_COLS - 1) / MC_COLS);
     if (a.T > a.B) {
       // some request brings several rows: 32 tokens at a time (single-token requests of the same step are chunks of one)
       static bool smem_set = false;
@@ -455,8 +547,8 @@ int mlstm_step(const MlstmArgs& a, cudaStream_t st) {
         KGE_CUDA_OK(cudaFuncSetAttribute(mlstm_chunk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         smem_set = true;
       }
-      if (a.elt == KGE_ELT_F32) KGE_CUDA_OK(launch_pdl(mlstm_chunk_kernel<float>, grid, dim3(ML_COLS * ML_NSL), csm_bytes, st, a));
-      else KGE_CUDA_OK(launch_pdl(mlstm_chunk_kernel<__nv_bfloat16>, grid, dim3(ML_COLS * ML_NSL), csm_bytes, st, a));
+      if (a.elt == KGE_ELT_F32) KGE_CUDA_OK(launch_pdl(mlstm_chunk_kernel<float>, cgrid, dim3(MC_COLS * ML_NSL), csm_bytes, st, a));
+      else KGE_CUDA_OK(launch_pdl(mlstm_chunk_kernel<__nv_bfloat16>, cgrid, dim3(MC_COLS * ML_NSL), csm_bytes, st, a));
       if (a.elt == KGE_ELT_F32) KGE_CUDA_OK(launch_pdl(mlstm_norm_gate_kernel<float>, g2, dim3(nt), 0, st, a));
       else KGE_CUDA_OK(launch_pdl(mlstm_norm_gate_kernel<__nv_bfloat16>, g2, dim3(nt), 0, st, a));
       return 0;
