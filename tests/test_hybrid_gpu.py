@@ -178,8 +178,9 @@ def test_chunk_edges_with_peaked_scores(kge, tmp_path, dtype, dims):
 
 
 def test_far_keys_tensor_core_kernel(kge, tmp_path):
-    """bfloat16, 48-wide heads, several key tiles per warp and a chunk edge in the middle of the prompt; grouped heads."""
-    cfg = oh.make_config(layers=("parallel",), mlps=(None,), right_scale=0.0, chunk=200, scale=0.6, heads=6, kv_heads=2, dim=48, vdim=48)
+    """bfloat16, 32-wide keys and 56-wide values, several key tiles per warp and a chunk edge in the middle of the prompt;
+    grouped heads."""
+    cfg = oh.make_config(layers=("parallel",), mlps=(None,), right_scale=0.0, chunk=200, scale=0.7, heads=6, kv_heads=2, dim=32, vdim=56)
     W = oh.make_weights(cfg, seed=15)
     toks = prompt(cfg, 290, 32)
     want = oh.forward(cfg, W, toks)
