@@ -276,3 +276,42 @@ def test_greedy_generation_through_the_scheduler(kge, tmp_path, dtype):
                 gap = float(lg[best] - lg[g])
                 assert gap < (1e-3 if dtype == "float32" else 0.15), f"token {k}: chose {g}, oracle {best} leads by {gap}"
             toks.append(g)
+
+
+def test_trace_runner_command_line(kge, tmp_path):
+    """bin/trace_run end to end: JSON steps on stdin (pieces of two requests side by side, a request that ends and one
+    that takes its slot and pages), float32 files out, 'done <step>' lines; and exit code 3 for a family without float32."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = oh.make_config(layers=("rglru", "parallel", "parallel"), mlps=("dense", "moe", None), chunk=24)
+    W = oh.make_weights(cfg, seed=17)
+    d = str(tmp_path / "m")
+    oh.save_model_dir(d, cfg, W)
+    P = {"a": prompt(cfg, 50, 80), "b": prompt(cfg, 31, 81), "c": prompt(cfg, 40, 82)}
+    want = {k: oh.forward(cfg, W, v).numpy() for k, v in P.items()}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": P["a"][:30], "want": [0, 29]}, {"id": "b", "tokens": P["b"][:2], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "b", "tokens": P["b"][2:], "want": [0, 28]}, {"id": "a", "tokens": P["a"][30:31], "want": [0]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": P["a"][31:], "want": [18]}, {"id": "c", "tokens": P["c"], "want": [39, 5]}], "end": ["a", "c"]},
+    ]
+    rows = {0: [("a", 0), ("a", 29)], 1: [("b", 2), ("b", 30), ("a", 30)], 2: [("a", 49), ("c", 39), ("c", 5)]}
+    for dtype in ("float32", "bfloat16"):
+        out = str(tmp_path / ("out_" + dtype))
+        r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", out, "--max-tokens", "128"],
+                           input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+        for st, rr in rows.items():
+            got = np.fromfile(os.path.join(out, f"{st}.f32"), dtype="<f4").reshape(len(rr), cfg["vocab"])
+            check(got, np.stack([want[k][i] for k, i in rr]), dtype, f"step {st}")
+    from oracle import model as om
+    lcfg = om.CONFIGS["tiny-llama"]
+    ld = str(tmp_path / "llama")
+    om.save_model_dir(ld, lcfg, om.make_weights(lcfg, seed=0))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", ld, "--dtype", "float32", "--out", str(tmp_path / "o2"),
+                        "--max-tokens", "128"], input="", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 3, (r.returncode, r.stderr[-500:])
+
