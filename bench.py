@@ -548,6 +548,27 @@ def design_configs(z):
     return hyb, lla
 
 
+GIROLORN_SIZES = {
+    # attention + mixture-of-experts layers (Girolorn) at sizes that resemble real layers; the Llama beside them has the same
+    # width, depth and heads, and a feed-forward as wide as what one Girolorn token runs through (top experts + shared expert)
+    "w2048": dict(width=2048, vocab=32000, own=4, shared_runs=4, heads=16, kv=4, dim=128, rot=64, experts=16, top=2, eff=1024, sff=2048, llama_ffn=4096),
+    "w4096": dict(width=4096, vocab=32000, own=4, shared_runs=0, heads=32, kv=8, dim=128, rot=128, experts=8, top=2, eff=3584, sff=3584, llama_ffn=10752),
+}
+
+
+def girolorn_configs(z):
+    mixer = {"dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv"], "vdim": z["dim"], "scale": z["dim"] ** -0.5, "softcap": 50.0,
+             "rot": {"base": 1000000.0, "dims": z["rot"], "scaling": {"factor": 16.0, "original": 4096, "fast": 24.0, "slow": 2.0}}}
+    moe = {"expert": {"ff": z["eff"], "limit": 7.0}, "kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["sff"], "limit": 7.0}}
+    layers = [{"mixer": mixer, "mlp": moe, "type": "attention"} for _ in range(z["own"])]
+    layers += [{"mixer": mixer, "mlp": moe, "type": "attention", "weights_of": i % z["own"]} for i in range(z["shared_runs"])]
+    gir = {"architecture": "Girolorn", "layers": layers, "logit_softcap": 25.0, "norm": {"eps": 1e-6}, "vocab": z["vocab"], "width": z["width"]}
+    lla = {"model_type": "llama", "vocab_size": z["vocab"], "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 8192,
+           "hidden_size": z["width"], "num_hidden_layers": len(layers), "intermediate_size": z["llama_ffn"], "num_attention_heads": z["heads"],
+           "num_key_value_heads": z["kv"], "head_dim": z["dim"], "tie_word_embeddings": False, "bos_token_id": 1, "eos_token_id": 2}
+    return gir, lla
+
+
 def time_raw_steps(kge, llm, batch_np, steps, warmup):
     """Wall-clock seconds per synchronous engine step (metadata upload, kernels, sampled ids back), after warm-up."""
     import ctypes as C
@@ -579,17 +600,19 @@ def raw_batch(B, ctx, q, bs, vocab, seed):
 
 
 def run_designs(args):
-    """--designs: the layer-list design next to a Llama of equal size (random weights): one prefill step of 4 x 2048 tokens,
+    """--designs [safupel|girolorn]: a layer-list design next to a Llama of equal size (random weights): one prefill step of 4 x 2048 tokens,
     one decode step of 64 requests at context 2048, wall-clock per step plus per-kernel device times against the roofline."""
     from kge_loader import load
     kge = load()
     kge.require_cuda()
     hbm, tf, src = peaks()
     B, ctx, PB, bs = 64, 2048, 4, args.block_size
-    for name, z in DESIGN_SIZES.items():
-        line = {"design_compare": name, "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+    which = args.designs
+    sizes, make, arms = (GIROLORN_SIZES, girolorn_configs, ("girolorn", "llama")) if which == "girolorn" else (DESIGN_SIZES, design_configs, ("safupel", "llama"))
+    for name, z in sizes.items():
+        line = {"design_compare": name, "design": which, "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
                 "prefill": f"{PB} x {ctx} tokens in one step", "decode": f"{B} requests, one token each at context {ctx}", "arms": {}}
-        for arm, cfg in zip(("safupel", "llama"), design_configs(z)):
+        for arm, cfg in zip(arms, make(z)):
             with tempfile.TemporaryDirectory() as d:
                 json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
                 llm = kge.LLM(d, load_format="dummy", seed=1, dtype="bfloat16", block_size=bs, max_model_len=ctx + 64, max_num_seqs=B,
@@ -646,7 +669,8 @@ def main():
     ap.add_argument("--no-tp", action="store_true", help="at N > 1, skip the tensor-parallel (config 4) sub-record")
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"], help="TP data path: peer memory (default) or NCCL")
     ap.add_argument("--tp-timeout", type=float, default=420.0, help="seconds the tensor-parallel leg may take at N > 1")
-    ap.add_argument("--designs", action="store_true", help="instead of the workload: the layer-list design (Safupel) beside a Llama of equal "
+    ap.add_argument("--designs", nargs="?", const="safupel", default=None, choices=["safupel", "girolorn"],
+                    help="instead of the workload: a layer-list design (safupel, the default, or girolorn) beside a Llama of equal "
                     "size, prefill and decode steps with per-kernel rooflines (one GPU, random weights)")
     args = ap.parse_args()
     args.warmup_ref = args.warmup        # same warm-up count as the GPU arm

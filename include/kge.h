@@ -118,6 +118,13 @@ int64_t kge_gemm_workspace_bytes(int T, int N, int K);
 int kge_gemm_silu_gate_bf16(void* y, const void* x, const void* w_gate_up, int T, int f, int K,
                             void* stream);
 /* the same with the optional split-K workspace of kge_gemm_bf16 (kge_gemm_workspace_bytes(T, f, K) bytes) */
+/* the gated front half with a clamped pair and a sigmoid gate: with g = min(x * w[:f]^T, limit) and
+ * u = clamp(x * w[f:]^T, -limit, limit) (both matrix products rounded to the 16-bit type first), y = g * sigmoid(alpha * g) * (u + 1).
+ * Same kernel, shapes and workspace as kge_gemm_silu_gate_ws_bf16. */
+int kge_gemm_clamped_glu_bf16(void* y, const void* x, const void* w_gate_up, int T, int f, int K, float alpha, float limit,
+                              void* workspace, int64_t workspace_bytes, void* stream);
+int kge_gemm_clamped_glu_f16(void* y, const void* x, const void* w_gate_up, int T, int f, int K, float alpha, float limit,
+                             void* workspace, int64_t workspace_bytes, void* stream);
 int kge_gemm_silu_gate_ws_bf16(void* y, const void* x, const void* w_gate_up, int T, int f, int K, void* workspace,
                                int64_t workspace_bytes, void* stream);
 

@@ -407,7 +407,7 @@ static int launch_attn(bf16* out, const bf16* q, int q_stride, const bf16* kc, c
 
 int paged_attn_prefill_tc(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc, const int32_t* bt,
                           int max_blocks, const int32_t* sl, const int32_t* qsl, int B, int max_q_len, int H, int KV,
-                          int hd, int bs, float scale, cudaStream_t st);   // attn_tc.cu
+                          int hd, int bs, float scale, float softcap, const float* sinks, cudaStream_t st);   // attn_tc.cu
 
 }  // namespace KGE_ELT_NS
 }  // namespace kge
@@ -438,7 +438,7 @@ extern "C" int KGE_API(kge_paged_attn)(void* out, const void* q, int q_stride, c
   KGE_REQUIRE(hd == 64 || hd == 128, "kge_paged_attn: head_dim=%d unsupported (64, 128)", hd);
   if (!(max_q_len == 1 && H / KV <= 16))
     return paged_attn_prefill_tc((bf16*)out, (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-                                 max_blocks_per_seq, seq_lens, query_start_loc, B, max_q_len, H, KV, hd, block_size, scale, st);
+                                 max_blocks_per_seq, seq_lens, query_start_loc, B, max_q_len, H, KV, hd, block_size, scale, 0.f, nullptr, st);
   if (hd == 64)
     return launch_attn<64>((bf16*)out, (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache,
                            block_table, max_blocks_per_seq, seq_lens, query_start_loc, B, max_q_len,

@@ -1,5 +1,5 @@
-// Paged attention with a linear distance bias per head and a chunk mask, for any key / value head size, in bfloat16 or
-// float32 storage.  One warp per (query row, head): 32 keys at a time, one key per lane for the scores (q in shared
+// Paged attention with a linear distance bias per head, a chunk mask, an optional soft cap of the scores and an optional
+// sink logit per head in the softmax denominator, for any key / value head size, in bfloat16 or float32 storage.  One warp per (query row, head): 32 keys at a time, one key per lane for the scores (q in shared
 // memory), softmax statistics in fp32 across the warp, then the lanes split the value columns.  Only keys of the
 // query's own chunk are read, so the cost per query is bounded by the chunk size whatever the context length.
 #include "common.cuh"
@@ -43,7 +43,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_bias_chunk_kernel(AttnBia
       const E* kr = kc + row * a.dim;
       float acc = 0.f;
       for (int d = 0; d < a.dim; ++d) acc = fmaf(qs[d], ldf(kr + d), acc);
-      s = acc * a.scale - slope * (float)(i - j);
+      acc *= a.scale;
+      if (a.softcap > 0.f) acc = a.softcap * tanhf(acc / a.softcap);
+      s = acc - slope * (float)(i - j);
     }
     const float mn = fmaxf(m, warp_max(s));
     const float p = valid ? expf(s - mn) : 0.f;
@@ -63,6 +65,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_bias_chunk_kernel(AttnBia
         if (col < a.vdim) o[c] = fmaf(pj, ldf(vr + col), o[c]);
       }
     }
+  }
+  if (a.sinks) {                                // the sink logit joins the denominator: no key, no value
+    const float sk = a.sinks[h], mn = fmaxf(m, sk), corr = expf(m - mn);
+    l = l * corr + expf(sk - mn);
+#pragma unroll
+    for (int c = 0; c < ATT_MAXV; ++c) o[c] *= corr;
   }
   const float inv = a.out_scale / l;
   E* out = (E*)a.out + (int64_t)t * a.ldo + h * a.vdim;
@@ -87,6 +95,10 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// tanh(x) = 1 - 2 / (e^(2x) + 1): absolute error of a few 1e-7 over the whole range (saturates cleanly at +-1)
+__device__ __forceinline__ float tanh_fast(float x) {
+  return 1.f - __fdividef(2.f, exp2f(fminf(x * 2.8853900817779268f, 100.f)) + 1.f);
 }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
@@ -138,6 +150,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
   const int own_first = wany ? a.positions[rs + R0 / hpg] : 0;
   const int own_lo = a.chunk > 0 ? (own_first / a.chunk) * a.chunk : 0;
   const float scale2 = a.scale * log2e;
+  const float cap2 = a.softcap * log2e, cap_in = a.softcap > 0.f ? a.scale / a.softcap : 0.f;   // capped scores, in units of log 2
   uint32_t qf[AM_MAXD / 16][4];
 #pragma unroll
   for (int ks = 0; ks < AM_MAXD / 16; ++ks) {
@@ -220,7 +233,9 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
       for (int c = 0; c < 4; ++c) {
         const int h = c >> 1, j = j0 + nt * 8 + qc + (c & 1);
         const bool vis = j <= pos[h] && j >= lo[h];
-        const float sv = vis ? sacc[nt][c] * scale2 - slope2[h] * (float)(pos[h] - j) : -INFINITY;
+        float sc = sacc[nt][c] * scale2;
+        if (cap2 > 0.f) sc = cap2 * tanh_fast(sacc[nt][c] * cap_in);
+        const float sv = vis ? sc - slope2[h] * (float)(pos[h] - j) : -INFINITY;
         sacc[nt][c] = sv;
         tmax[h] = fmaxf(tmax[h], sv);
       }
@@ -275,7 +290,13 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       if (pos[h] < 0) continue;
-      const float inv = a.out_scale / l[h];
+      float oc = 1.f;
+      if (a.sinks) {
+        const float sk = a.sinks[head[h]] * log2e, mn = fmaxf(m[h], sk);
+        oc = exp2f(m[h] - mn);
+        l[h] = l[h] * oc + exp2f(sk - mn);
+      }
+      const float inv = a.out_scale * oc / l[h];
       E* out = (E*)a.out + (int64_t)tok[h] * a.ldo + head[h] * vdim + qc;
 #pragma unroll
       for (int v = 0; v < AM_MAXD / 8; ++v)
@@ -305,7 +326,13 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < AM_WARPS; ++w) M = fmaxf(M, ML[(w * 2) * 16 + r]);
+    const int row = R0 + r;
     float num = 0.f, den = 0.f;
+    if (a.sinks) {
+      const float sk = a.sinks[g * hpg + row % hpg] * log2e;
+      M = fmaxf(M, sk);
+      den = exp2f(sk - M);
+    }
 #pragma unroll
     for (int w = 0; w < AM_WARPS; ++w) {
       const float mw = ML[(w * 2) * 16 + r];
@@ -313,7 +340,6 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
       num = fmaf(f, reinterpret_cast<const float*>(am_smem + w * region)[r * vdim + c], num);
       den = fmaf(f, ML[(w * 2 + 1) * 16 + r], den);
     }
-    const int row = R0 + r;
     E* out = (E*)a.out + (int64_t)(rs + row / hpg) * a.ldo + (g * hpg + row % hpg) * vdim + c;
     *out = __float2bfloat16_rn(num / den * a.out_scale);
   }

@@ -118,13 +118,25 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 constexpr float kRescaleThreshold = 8.0f;
 __device__ __forceinline__ float ex2_ftz(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
-template <int HD, bool TMA>
+// CAP: scores are soft-capped before the softmax, s <- cap * tanh(scale * s / cap); the kernel then works on capped
+// scores in units of log 2 (cap_log2 = cap * log2(e), cap_in = scale / cap).  tanh(y) = 1 - 2 / (e^(2y) + 1): two more
+// special-function operations per score than the plain kernel, absolute error of a few 1e-7.
+// sinks (fp32 [H], or null): exp(sinks[head]) joins a row's softmax denominator - a logit with no key and no value.
+__device__ __forceinline__ float rcp_ftz(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float capped_log2(float s, float cap_in2, float cap_log2) {
+  // cap_in2 = 2 log2(e) scale / cap: e^(2y) = 2^(s * cap_in2), clamped so that the quotient stays finite
+  const float e = ex2_ftz(fminf(s * cap_in2, 100.f));
+  return fmaf(-2.f * cap_log2, rcp_ftz(e + 1.f), cap_log2);
+}
+
+template <int HD, bool TMA, bool CAP = false>
 __global__ void __launch_bounds__(TMA ? 192 : 160, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                bf16* __restrict__ out, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
                const bf16* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
                const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ qsl, int H, int KV, int bs_shift,
-               float scale_log2) {
+               float scale_log2_in, float cap_in2, float cap_log2, const float* __restrict__ sinks) {
+  const float scale_log2 = CAP ? 1.f : scale_log2_in;    // capped scores are formed in units of log 2
   constexpr int CH = HD / 8;                       // 16-byte chunks per row
   constexpr uint32_t Q_BYTES = 128 * HD * 2;
   constexpr uint32_t TILE_BYTES = BNK * HD * 2;    // K or V tile
@@ -341,11 +353,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
       float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (__all_sync(0xffffffffu, kbase + BNK - 1 <= lim)) {
 #pragma unroll
-        for (int i = 0; i < BNK; ++i) mxa[i & 3] = fmaxf(mxa[i & 3], __uint_as_float(sv[i]));
+        for (int i = 0; i < BNK; ++i) {
+          if (CAP) sv[i] = __float_as_uint(capped_log2(__uint_as_float(sv[i]), cap_in2, cap_log2));
+          mxa[i & 3] = fmaxf(mxa[i & 3], __uint_as_float(sv[i]));
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < BNK; ++i) {
-          const float x = (kbase + i <= lim) ? __uint_as_float(sv[i]) : -INFINITY;
+          const float raw = CAP ? capped_log2(__uint_as_float(sv[i]), cap_in2, cap_log2) : __uint_as_float(sv[i]);
+          const float x = (kbase + i <= lim) ? raw : -INFINITY;
           sv[i] = __float_as_uint(x);
           mxa[i & 3] = fmaxf(mxa[i & 3], x);
         }
@@ -401,6 +417,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     tc_after();
     {
       // tcgen05.ld is warp-collective (.sync.aligned): every lane loads, only rows with a token store
+      if (sinks && row_ok && m_ref != -INFINITY) l += exp2f(sinks[kvh * G + hh] * kLog2e - m_ref);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = out + (int64_t)(q0 + tok0 + (row_ok ? tk : 0)) * H * HD + (kvh * G + hh) * HD;
 #pragma unroll 1
@@ -438,7 +455,9 @@ int make_tmap(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int b
 template <int HD>
 static int launch_tc(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc, const int32_t* bt,
                      int max_blocks, const int32_t* sl, const int32_t* qsl, int B, int max_q_len, int H, int KV, int bs,
-                     float scale, cudaStream_t st) {
+                     float scale, float softcap, const float* sinks, cudaStream_t st) {
+  const bool cap = softcap > 0.f;
+  const float cap_in2 = cap ? 2.f * atc::kLog2e * scale / softcap : 0.f, cap_log2 = softcap * atc::kLog2e;
   int bs_shift = 0;
   while ((1 << bs_shift) < bs) ++bs_shift;
   const int G = H / KV;
@@ -450,27 +469,27 @@ static int launch_tc(bf16* out, const bf16* q, int q_stride, const bf16* kc, con
     const int64_t rows = (int64_t)1 << 30;      // the pool's extent is not known here; it only bounds out-of-range handling, never relied on
     if (int rc = make_tmap(&tk, kc, rows, HD, box_rows)) return rc;
     if (int rc = make_tmap(&tv, vc, rows, HD, box_rows)) return rc;
-    auto kern = atc::attn_tc_kernel<HD, true>;
+    auto kern = cap ? atc::attn_tc_kernel<HD, true, true> : atc::attn_tc_kernel<HD, true, false>;
     KGE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::tc_smem<HD>()));
     KGE_CUDA_OK(launch_pdl(kern, dim3((max_q_len + TT - 1) / TT, KV, B), dim3(192), atc::tc_smem<HD>(), st, tk, tv, out, q, q_stride,
-                           kc, vc, bt, max_blocks, sl, qsl, H, KV, bs_shift, scale * atc::kLog2e));
+                           kc, vc, bt, max_blocks, sl, qsl, H, KV, bs_shift, scale * atc::kLog2e, cap_in2, cap_log2, sinks));
     return 0;
   }
   memset(&tk, 0, sizeof tk); memset(&tv, 0, sizeof tv);
-  auto kern = atc::attn_tc_kernel<HD, false>;
+  auto kern = cap ? atc::attn_tc_kernel<HD, false, true> : atc::attn_tc_kernel<HD, false, false>;
   KGE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::tc_smem<HD>()));
   KGE_CUDA_OK(launch_pdl(kern, dim3((max_q_len + TT - 1) / TT, KV, B), dim3(160), atc::tc_smem<HD>(), st, tk, tv, out, q, q_stride, kc,
-                         vc, bt, max_blocks, sl, qsl, H, KV, bs_shift, scale * atc::kLog2e));
+                         vc, bt, max_blocks, sl, qsl, H, KV, bs_shift, scale * atc::kLog2e, cap_in2, cap_log2, sinks));
   return 0;
 }
 
 // Called by kge_paged_attn (attn.cu) for batches with query chunks longer than one token.
 int paged_attn_prefill_tc(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc, const int32_t* bt,
                           int max_blocks, const int32_t* sl, const int32_t* qsl, int B, int max_q_len, int H, int KV,
-                          int hd, int bs, float scale, cudaStream_t st) {
+                          int hd, int bs, float scale, float softcap, const float* sinks, cudaStream_t st) {
   KGE_REQUIRE(H / KV <= 128, "kge_paged_attn: GQA group %d > 128 unsupported", H / KV);
-  if (hd == 128) return launch_tc<128>(out, q, q_stride, kc, vc, bt, max_blocks, sl, qsl, B, max_q_len, H, KV, bs, scale, st);
-  return launch_tc<64>(out, q, q_stride, kc, vc, bt, max_blocks, sl, qsl, B, max_q_len, H, KV, bs, scale, st);
+  if (hd == 128) return launch_tc<128>(out, q, q_stride, kc, vc, bt, max_blocks, sl, qsl, B, max_q_len, H, KV, bs, scale, softcap, sinks, st);
+  return launch_tc<64>(out, q, q_stride, kc, vc, bt, max_blocks, sl, qsl, B, max_q_len, H, KV, bs, scale, softcap, sinks, st);
 }
 
 }  // namespace KGE_ELT_NS

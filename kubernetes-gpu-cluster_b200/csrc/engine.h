@@ -62,6 +62,16 @@ struct HybridLayerW {
   HybMat proj, gates, o2;
   int off_k = 0, off_v = 0, off_mq = 0, off_mk = 0, off_mv = 0, off_mg = 0;
   void* m_norm = nullptr;
+  // attention mixer: [q | k] projection (values may be the key projection itself), weights of the RMS norms over the whole
+  // q and k projections, sink logits (fp32 [heads]), rotary frequencies (double [rot_dims / 2]) and their cos / sin multiplier
+  HybMat qk;
+  void *q_norm = nullptr, *k_norm = nullptr;
+  float* sinks = nullptr;
+  double* rot_freq = nullptr;
+  float rot_mult = 1.f;
+  void* norm2 = nullptr;                      // models whose feed-forward reads a norm of its own
+  void* router_b = nullptr;                   // router bias
+  void* s_sg = nullptr;                       // [d]: the shared expert's per-token sigmoid gate
   void *kc = nullptr, *vc = nullptr;          // paged caches of the attention side
   // feed-forward: dense (up, down) or experts ([E, ff, d] gate and up, [E, d, ff] down) + router (+ shared expert)
   HybMat up, down, router, s_gate, s_up, s_down;

@@ -1,6 +1,7 @@
 // Layer-list ("hybrid") models in the engine: a config.json that lists its layers, each with a token mixer (gated
-// linear recurrence, or attention and a matrix memory side by side) and a feed-forward (dense or mixture of experts),
-// both reading ONE norm of an fp32 residual stream.  This file loads such a model (weights in the engine's storage
+// linear recurrence, attention and a matrix memory side by side, or attention alone with rotary positions, a soft cap
+// and sink logits) and a feed-forward (dense or mixture of experts), reading ONE norm of an fp32 residual stream or a
+// norm each in sequence.  This file loads such a model (weights in the engine's storage
 // type, fused where one activation feeds several projections), sizes its arena, paged caches and recurrent-state pool,
 // and runs its step: the same flattened batch, block tables and slot mapping as every other model, plus a state slot
 // per request.  Nothing here depends on how a prompt was cut into steps: recurrences continue from the slot, attention
@@ -17,6 +18,12 @@
 using namespace kge;
 
 namespace kge {
+inline namespace b16 {
+// attn_tc.cu: tcgen05 attention over query chunks (64- and 128-wide heads, bfloat16), optional soft cap and sink logits
+int paged_attn_prefill_tc(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc, const int32_t* bt, int max_blocks,
+                          const int32_t* sl, const int32_t* qsl, int B, int max_q_len, int H, int KV, int hd, int bs, float scale, float softcap,
+                          const float* sinks, cudaStream_t st);
+}
 
 namespace {
 
@@ -55,6 +62,20 @@ struct HB {
     }
     if (ce != cudaSuccess) { err = "cudaMemcpy of weights failed"; return nullptr; }
     return p;
+  }
+  // arrays kept in one type whatever the engine's storage type (sink logits, rotary frequencies)
+  template <typename T>
+  T* upload_raw(const std::vector<T>& v) {
+    T* p = (T*)dalloc((int64_t)v.size(), sizeof(T));
+    if (!p) return nullptr;
+    e->weight_bytes += (int64_t)v.size() * sizeof(T);
+    if (cudaMemcpy(p, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice) != cudaSuccess) { err = "cudaMemcpy of weights failed"; return nullptr; }
+    return p;
+  }
+  float* vec_f32(const std::string& name, int64_t n, float dummy_const) {
+    std::vector<float> v((size_t)n, dummy_const);
+    if (!dummy() && !stack({name}, {n}, 1, &v)) return nullptr;
+    return upload_raw(v);
   }
   // tensors stacked along their first dimension; every one must have `inner` elements per leading index
   bool stack(const std::vector<std::string>& names, const std::vector<int64_t>& lead, int64_t inner, std::vector<float>* out) {
@@ -104,7 +125,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
 #define HB_OK(p) do { if (!(p)) return fail(b.err); } while (0)
   HB_OK(e->embed = (bf16*)b.mat({"embed"}, {s.vocab}, d, ws));
   HB_OK(e->lm_head = (bf16*)b.mat({"head"}, {s.vocab}, d, ws));
-  HB_OK(e->final_w = (bf16*)b.mat({"final.norm"}, {d}, 1, 0.f, 0.f));
+  HB_OK(e->final_w = (bf16*)b.mat({"final.norm"}, {d}, 1, 0.f, s.hyb_layernorm ? 1.f : 0.f));
   e->hyb.resize(s.L);
   int64_t state_floats = 0;
   int max_mo = 1;
@@ -113,7 +134,15 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
     const HybridLayerSpec& h = s.hybrid[i];
     HybridLayerW& L = e->hyb[i];
     const std::string p = "l" + std::to_string(i) + ".", mx = p + "mix.", fp = p + "mlp.";
-    HB_OK(L.norm1 = b.mat({p + "norm1"}, {d}, 1, 0.f, 0.f));
+    if (h.weights_of >= 0) {                   // another layer's tensors; the paged caches below stay this layer's own
+      L = e->hyb[h.weights_of];
+      L.kc = L.vc = nullptr;
+      L.state_off = state_floats;
+      continue;
+    }
+    const float norm_one = s.hyb_layernorm ? 1.f : 0.f;      // the weight that leaves the normed row as it is
+    HB_OK(L.norm1 = b.mat({p + "norm1"}, {d}, 1, 0.f, norm_one));
+    if (s.hyb_prenorm_pair && h.mlp != HybridLayerSpec::NONE) HB_OK(L.norm2 = b.mat({p + "norm2"}, {d}, 1, 0.f, norm_one));
     L.state_off = state_floats;
     if (h.mixer == HybridLayerSpec::RGLRU) {
       const int w = h.width, bw = w / h.blocks;
@@ -132,6 +161,24 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
       HB_OK(L.o.w = b.mat({mx + "o"}, {d}, w, ws));
       state_floats += rglru_state_floats(w, h.conv);
       max_proj = std::max(max_proj, 2 * w); max_mix = std::max(max_mix, w); max_gate = std::max(max_gate, 2 * w); max_u = std::max(max_u, w);
+    } else if (h.mixer == HybridLayerSpec::ATTENTION) {
+      const int nq = h.heads * h.dim, nk = h.kv_heads * h.dim;
+      if (!h.v_from_k) return fail("an attention mixer with a value projection of its own is not built");
+      L.qk.N = nq + nk; L.qk.K = d;
+      HB_OK(L.qk.w = b.mat({mx + "q", mx + "k"}, {nq, nk}, d, ws));
+      if (h.qk_norm) {
+        HB_OK(L.q_norm = b.mat({mx + "q.norm"}, {nq}, 1, 0.f, 1.f));
+        HB_OK(L.k_norm = b.mat({mx + "k.norm"}, {nk}, 1, 0.f, 1.f));
+      }
+      if (h.sink) HB_OK(L.sinks = b.vec_f32(mx + "sink", h.heads, 0.f));
+      if (h.rot_dims > 0) {
+        std::vector<double> fr((size_t)h.rot_dims / 2);
+        rotary_frequencies(h.rot_dims, h.rot_base, h.yarn_factor, h.yarn_original, h.yarn_fast, h.yarn_slow, fr.data(), &L.rot_mult);
+        HB_OK(L.rot_freq = b.upload_raw(fr));
+      }
+      L.o.N = d; L.o.K = h.heads * h.vdim;
+      HB_OK(L.o.w = b.mat({mx + "o"}, {d}, h.heads * h.vdim, ws));
+      max_proj = std::max(max_proj, L.qk.N); max_mix = std::max(max_mix, L.o.K);
     } else {
       const int nq = h.heads * h.dim, nk = h.kv_heads * h.dim, nv = h.kv_heads * h.vdim, mq = h.m_heads * h.m_dim, mv = h.m_heads * h.m_vdim;
       L.off_k = nq; L.off_v = nq + nk; L.off_mq = L.off_v + nv; L.off_mk = L.off_mq + mq; L.off_mv = L.off_mk + mq; L.off_mg = L.off_mv + mv;
@@ -167,6 +214,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
     } else if (h.mlp == HybridLayerSpec::MOE) {
       L.router.N = h.experts; L.router.K = d;
       HB_OK(L.router.w = b.mat({fp + "router"}, {h.experts}, d, ws * 4));
+      if (h.router_bias) HB_OK(L.router_b = b.mat({fp + "router.b"}, {h.experts}, 1, 0.f, 0.f));
       // per expert [gate | up] rows in one block (what the fused gated GEMM reads), then all experts' down matrices
       std::vector<std::string> gu, dn;
       std::vector<int64_t> lf((size_t)2 * h.experts, h.expert_ff), ld((size_t)h.experts, d);
@@ -180,6 +228,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
         HB_OK(L.s_gate.w = b.mat({fp + "shared.gate", fp + "shared.up"}, {h.shared_ff, h.shared_ff}, d, ws));
         L.s_up.w = (uint8_t*)L.s_gate.w + (int64_t)h.shared_ff * d * b.esz();
         HB_OK(L.s_down.w = b.mat({fp + "shared.down"}, {d}, h.shared_ff, ws));
+        if (h.shared_gate) HB_OK(L.s_sg = b.mat({fp + "shared.sg"}, {1}, d, ws));
         max_ff = std::max(max_ff, h.shared_ff);
       }
       max_top = std::max(max_top, h.top); max_eff = std::max(max_eff, h.expert_ff); max_E = std::max(max_E, h.experts);
@@ -246,7 +295,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   // paged caches of the attention sides: K [blocks, G, block_size, dim], V [blocks, G, block_size, vdim] per layer
   int64_t blk_bytes = 0;
   for (auto& h : s.hybrid)
-    if (h.mixer == HybridLayerSpec::PARALLEL) blk_bytes += (int64_t)h.kv_heads * e->cfg.block_size * (h.dim + h.vdim) * es;
+    if (h.mixer != HybridLayerSpec::RGLRU) blk_bytes += (int64_t)h.kv_heads * e->cfg.block_size * (h.dim + h.vdim) * es;
   int nb = e->cfg.num_blocks;
   if (nb <= 0) {
     const int64_t cap = (int64_t)e->cfg.max_num_seqs * e->max_blocks_per_seq + 1;
@@ -267,7 +316,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   e->kv_bytes = blk_bytes * nb;
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
-    if (h.mixer != HybridLayerSpec::PARALLEL) continue;
+    if (h.mixer == HybridLayerSpec::RGLRU) continue;
     const int64_t nk = (int64_t)nb * h.kv_heads * e->cfg.block_size * h.dim, nv = (int64_t)nb * h.kv_heads * e->cfg.block_size * h.vdim;
     e->hyb[i].kc = aalloc(nk, es); e->hyb[i].vc = aalloc(nv, es);
     if (!e->hyb[i].kc || !e->hyb[i].vc) return fail("KV pool allocation failed");
@@ -338,13 +387,20 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
   // launch buys nothing there, and hundreds of long-running CTAs of one kernel waiting on the previous one would only
   // hold shared memory.  Decode steps keep programmatic dependent launch (and run as CUDA graphs).
   struct PdlOff { bool on; explicit PdlOff(bool o) : on(o) { if (on) pdl_suspend(true); } ~PdlOff() { if (on) pdl_suspend(false); } } pdl_off(!decode_only);
+  // the model's norm of residual rows: RMS with the weight applied as 1 + w, or the weight-only layer norm
+  auto layer_norm = [&](void* y, const int32_t* rows, const void* w, int R, float out_scale) -> int {
+    return s.hyb_layernorm ? layernorm_f32in(y, e->res32, rows, w, R, d, s.eps, out_scale, elt, st)
+                           : rmsnorm_f32in(y, e->res32, rows, w, R, d, s.eps, 1.f, out_scale, elt, st);
+  };
   HFWD(C_EMBED, Td * (es + 4), 0, embed_f32(e->res32, m.ids, e->embed, T, d, elt, st));
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
     const HybridLayerW& L = e->hyb[i];
-    HFWD(C_NORM, Td * (4 + es), 0, rmsnorm_f32in(e->hx, e->res32, nullptr, L.norm1, T, d, s.eps, 1.f, 1.f, elt, st));
+    HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm1, T, 1.f));
     CombineArgs cb;
-    auto add_src = [&](const void* p, int ld, float scale) { cb.src[cb.n] = p; cb.ld[cb.n] = ld; cb.scale[cb.n] = scale; ++cb.n; };
+    auto add_src = [&](const void* p, int ld, float scale, const float* rscale = nullptr, int rs_stride = 0) {
+      cb.src[cb.n] = p; cb.ld[cb.n] = ld; cb.scale[cb.n] = scale; cb.rscale[cb.n] = rscale; cb.rs_stride[cb.n] = rs_stride; ++cb.n;
+    };
     auto flush = [&]() -> int { if (cb.n == 0) return 0; int rc = residual_combine(e->res32, cb, T, d, elt, st); cb = CombineArgs(); return rc; };
     if (h.mixer == HybridLayerSpec::RGLRU) {
       const int w = h.width, bw = w / h.blocks;
@@ -367,6 +423,34 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       }
       HFWD(C_RGLRU, Tw * (3 * es + 8) + 2.0 * B * rglru_state_floats(w, h.conv) * 4, 0, rglru_scan(ra, st));
       DENSE(e->obuf1, d, e->mixbuf, w, L.o, T, ACT_NONE);
+      add_src(e->obuf1, d, 1.f);
+    } else if (h.mixer == HybridLayerSpec::ATTENTION) {
+      const int nq = h.heads * h.dim, ldp = L.qk.N, ko = L.o.K;
+      DENSE(e->pbuf, ldp, e->hx, d, L.qk, T, ACT_NONE);
+      RotaryArgs ro;     // norm over the whole q and k projections, rotation, K cache <- rotated keys, V cache <- the raw key projection
+      ro.q = e->pbuf; ro.ldq = ldp; ro.k = at(e->pbuf, nq); ro.ldk = ldp; ro.q_norm_w = L.q_norm; ro.k_norm_w = L.k_norm; ro.eps = s.eps;
+      ro.freq = L.rot_freq; ro.mult = L.rot_mult; ro.rot_dims = h.rot_dims; ro.positions = m.pos; ro.slots = m.slots;
+      ro.k_cache = L.kc; ro.v_cache = L.vc; ro.T = T; ro.H = h.heads; ro.G = h.kv_heads; ro.dim = h.dim; ro.vdim = h.vdim; ro.block_size = bs; ro.elt = elt;
+      HFWD(C_KVW, (double)T * (2.0 * nq + 3.0 * h.kv_heads * h.dim) * es, 0, rotary_norm_kvwrite(ro, st));
+      AttnBiasArgs aa;
+      aa.q = e->pbuf; aa.ldq = ldp; aa.out = e->mixbuf; aa.ldo = ko; aa.k_cache = L.kc; aa.v_cache = L.vc;
+      aa.block_table = m.btab; aa.max_blocks = max_blocks; aa.seq_lens = m.seq_lens; aa.qsl = m.qsl; aa.positions = m.pos; aa.token_req = m.treq;
+      aa.B = B; aa.T = T; aa.H = h.heads; aa.G = h.kv_heads; aa.dim = h.dim; aa.vdim = h.vdim; aa.block_size = bs; aa.chunk = 0;
+      aa.scale = h.scale; aa.bias_span = 0.f; aa.softcap = h.softcap; aa.sinks = L.sinks; aa.elt = elt;
+      for (int r = 0; r < B; ++r) aa.max_q = std::max(aa.max_q, hm.qsl[r + 1] - hm.qsl[r]);
+      while (aa.num_decode < B && hm.qsl[aa.num_decode + 1] - hm.qsl[aa.num_decode] == 1) ++aa.num_decode;
+      double keys = 0;                                   // visible keys over all rows
+      for (int t = 0; t < T; ++t) keys += hm.pos[t] + 1;
+      // steps with prompt pieces, 64- / 128-wide heads, bfloat16: the tcgen05 kernel of the Llama family (TMA-staged K/V
+      // tiles, S and O in TMEM) with the cap and the sinks; everything else: the mma.sync / per-row kernels
+      const bool tc = !e->f32 && !decode_only && (h.dim == 64 || h.dim == 128) && h.vdim == h.dim && ldp % 8 == 0 && (bs & (bs - 1)) == 0 &&
+                      h.heads / h.kv_heads <= 128 && ((uintptr_t)e->pbuf & 15) == 0;
+      HFWD(decode_only ? C_ATT_DEC : C_ATT_GEN, (decode_only ? keys : (double)T) * h.kv_heads * (h.dim + h.vdim) * es + (double)T * h.heads * (h.dim + h.vdim) * es,
+           2.0 * keys * h.heads * (h.dim + h.vdim),
+           tc ? paged_attn_prefill_tc((bf16*)e->mixbuf, (const bf16*)e->pbuf, ldp, (const bf16*)L.kc, (const bf16*)L.vc, m.btab, max_blocks, m.seq_lens, m.qsl,
+                                      B, aa.max_q, h.heads, h.kv_heads, h.dim, bs, h.scale, h.softcap, L.sinks, st)
+              : attn_bias_chunk(aa, st));
+      DENSE(e->obuf1, d, e->mixbuf, ko, L.o, T, ACT_NONE);
       add_src(e->obuf1, d, 1.f);
     } else {
       const int ka = h.heads * h.vdim, ko = L.o2.K, ldp = L.proj.N;
@@ -401,13 +485,21 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       DENSE(e->obuf1, d, e->mixbuf, ko, L.o2, T, ACT_NONE);
       add_src(e->obuf1, d, 1.f);
     }
+    if (s.hyb_prenorm_pair && h.mlp != HybridLayerSpec::NONE) {
+      // the feed-forward reads a norm of the stream that already holds the mixer's output
+      { const double nsrc = cb.n; HFWD(C_ACT, Td * (8 + nsrc * es), 0, flush()); }
+      HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm2, T, 1.f));
+    }
     if (h.mlp == HybridLayerSpec::DENSE) {
       DENSE(e->ffbuf, h.ff, e->hx, d, L.up, T, ACT_GELU_ERF);
       DENSE(e->obuf2, d, e->ffbuf, h.ff, L.down, T, ACT_NONE);
       add_src(e->obuf2, d, 1.f);
     } else if (h.mlp == HybridLayerSpec::MOE) {
       MoeRouteArgs ra;
-      ra.h = e->hx; ra.ldh = d; ra.w_router = L.router.w; ra.T = T; ra.d = d; ra.E = h.experts; ra.top = h.top; ra.score_fn = 0; ra.renorm = false;
+      ra.h = e->hx; ra.ldh = d; ra.w_router = L.router.w; ra.b_router = L.router_b; ra.T = T; ra.d = d; ra.E = h.experts; ra.top = h.top;
+      const bool w_out = h.route == HybridLayerSpec::ROUTE_SOFTMAX_TOP;      // the routing weight multiplies the expert's output (in the fp32 sum below)
+      const bool clamped = h.glu == HybridLayerSpec::GLU_CLAMPED;
+      ra.score_fn = w_out ? 2 : 0; ra.renorm = false;
       ra.group_off = e->moe_goff; ra.perm_token = e->moe_ptok; ra.perm_weight = e->moe_pw; ra.perm_dest = e->moe_pdest;
       ra.choice_expert = e->moe_cexp; ra.choice_weight = e->moe_cw; ra.elt = elt;
       HFWD(C_MOE, Td * es + (double)h.experts * d * es, 2.0 * Td * h.experts, moe_route(ra, st));
@@ -419,7 +511,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
         // (gated front half with SiLU*mul in the epilogue, then down) on its own rows; the row counts come to the host
         // once per layer - a few microseconds beside milliseconds of expert work
         const int eff = h.expert_ff;
-        HFWD(C_MOE, (double)np * d * 4, 0, moe_gather_rows(e->moe_xperm, e->hx, d, e->moe_ptok, e->moe_pw, np, d, st));
+        HFWD(C_MOE, (double)np * d * 4, 0, moe_gather_rows(e->moe_xperm, e->hx, d, e->moe_ptok, w_out ? nullptr : e->moe_pw, np, d, st));
         KGE_CUDA_OK(cudaMemcpyAsync(e->moe_goff_host, e->moe_goff, (size_t)(h.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
         KGE_CUDA_OK(cudaStreamSynchronize(st));
         for (int x = 0; x < h.experts; ++x) {
@@ -428,7 +520,8 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
           const uint8_t* wgu = (const uint8_t*)L.e_gate + (int64_t)x * 2 * eff * d * 2;
           const uint8_t* wdn = (const uint8_t*)L.e_down + (int64_t)x * d * eff * 2;
           HFWD(cnt <= 256 ? C_GEMM_S : C_MOE, 2.0 * (2.0 * eff * d + (double)cnt * (d + eff)), 4.0 * cnt * (double)eff * d,
-               kge_gemm_silu_gate_ws_bf16(at(e->moe_hidden, (int64_t)off * eff), at(e->moe_xperm, (int64_t)off * d), wgu, cnt, eff, d, nullptr, 0, st));
+               clamped ? kge_gemm_clamped_glu_bf16(at(e->moe_hidden, (int64_t)off * eff), at(e->moe_xperm, (int64_t)off * d), wgu, cnt, eff, d, 1.702f, h.expert_limit, nullptr, 0, st)
+                       : kge_gemm_silu_gate_ws_bf16(at(e->moe_hidden, (int64_t)off * eff), at(e->moe_xperm, (int64_t)off * d), wgu, cnt, eff, d, nullptr, 0, st));
           HFWD(cnt <= 256 ? C_GEMM_S : C_MOE, 2.0 * ((double)eff * d + (double)cnt * (d + eff)), 2.0 * cnt * (double)eff * d,
                kge_gemm_bf16(at(e->moe_operm, (int64_t)off * d), at(e->moe_hidden, (int64_t)off * eff), wdn, nullptr, cnt, d, eff, 0, nullptr, 0, st));
         }
@@ -436,7 +529,8 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       } else {
       LinearArgs g;      // experts' gated front half on the gathered, weighted rows
       g.x = e->hx; g.ldx = d; g.w = L.e_gate; g.w2 = L.e_up; g.y = e->moe_hidden; g.ldy = h.expert_ff; g.T = np; g.N = h.expert_ff; g.K = d;
-      g.nz = h.experts; g.w_zs = (int64_t)2 * h.expert_ff * d; g.group_off = e->moe_goff; g.max_rows = np; g.xrows = e->moe_ptok; g.row_scale = e->moe_pw;
+      g.nz = h.experts; g.w_zs = (int64_t)2 * h.expert_ff * d; g.group_off = e->moe_goff; g.max_rows = np; g.xrows = e->moe_ptok; g.row_scale = w_out ? nullptr : e->moe_pw;
+      if (clamped) { g.glu = GLU_CLAMPED_SIGMOID; g.glu_limit = h.expert_limit; }
       g.elt = elt; g.out_f32 = e->f32;
       HFWD(C_MOE, 2 * wexp + (double)np * (d + h.expert_ff) * es, 4.0 * np * (double)h.expert_ff * d, linear_any(g, st));
       LinearArgs dn;     // experts' down projection, scattered to row (token * top + choice)
@@ -449,22 +543,30 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
         const int f = h.shared_ff;
         const double gb = es * (2.0 * f * d + (double)T * (d + f)), gf = 4.0 * T * (double)f * d;
         if (!e->f32 && f % 64 == 0 && d % 8 == 0) {
-          // [T, 2f] never reaches memory: SiLU * mul in the epilogue of the tensor-core GEMM
-          HFWD(T <= 256 ? C_GEMM_S : C_GEMM_L, gb, gf, kge_gemm_silu_gate_ws_bf16(e->ffbuf, e->hx, L.s_gate.w, T, f, d, nullptr, 0, st));
+          // [T, 2f] never reaches memory: the gated pair is formed in the epilogue of the tensor-core GEMM
+          HFWD(T <= 256 ? C_GEMM_S : C_GEMM_L, gb, gf,
+               clamped ? kge_gemm_clamped_glu_bf16(e->ffbuf, e->hx, L.s_gate.w, T, f, d, 1.702f, h.shared_limit, nullptr, 0, st)
+                       : kge_gemm_silu_gate_ws_bf16(e->ffbuf, e->hx, L.s_gate.w, T, f, d, nullptr, 0, st));
         } else {
           LinearArgs sg;
           sg.x = e->hx; sg.ldx = d; sg.w = L.s_gate.w; sg.w2 = L.s_up.w; sg.y = e->ffbuf; sg.ldy = f; sg.T = T; sg.N = f; sg.K = d;
+          if (clamped) { sg.glu = GLU_CLAMPED_SIGMOID; sg.glu_limit = h.shared_limit; }
           sg.elt = elt; sg.out_f32 = e->f32;
           HFWD(T <= 256 ? C_GEMM_S : C_GEMM_L, gb, gf, linear_any(sg, st));
         }
         DENSE(e->obuf2, d, e->ffbuf, f, L.s_down, T, ACT_NONE);
+        if (L.s_sg) {        // one sigmoid gate per token, kept in fp32 and applied in the residual sum
+          LinearArgs a;
+          a.x = e->hx; a.ldx = d; a.w = L.s_sg; a.y = e->gates32; a.ldy = 1; a.T = T; a.N = 1; a.K = d; a.act = ACT_SIGMOID; a.elt = elt; a.out_f32 = true;
+          HFWD(C_MOE, Td * es, 2.0 * Td, linear_any(a, st));
+        }
       }
       // sum in a fixed order: mixer, the token's experts by choice, the shared expert
       for (int k = 0; k < h.top; ++k) {
         if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush());
-        add_src(at(e->moe_out, (int64_t)k * d), h.top * d, 1.f);
+        add_src(at(e->moe_out, (int64_t)k * d), h.top * d, 1.f, w_out ? e->moe_cw + k : nullptr, h.top);
       }
-      if (h.shared_ff > 0) { if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush()); add_src(e->obuf2, d, 1.f); }
+      if (h.shared_ff > 0) { if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush()); add_src(e->obuf2, d, 1.f, L.s_sg ? e->gates32 : nullptr, 1); }
     }
     { const double nsrc = cb.n; HFWD(C_ACT, Td * (8 + nsrc * es), 0, flush()); }
     if (e->layer_dump_host && (int64_t)(i + 1) * T * d <= e->layer_dump_cap) {
@@ -478,15 +580,17 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
     const double hb = es * ((double)s.vocab * d + (double)R * (d + s.vocab)), hf = 2.0 * R * (double)s.vocab * d;
     if (e->hyb_head_tc) {
       // norm (the logits' multiplier folded into it), then the tensor-core GEMM straight into the 16-bit logits
-      HFWD(C_NORM, (double)R * d * (4 + es), 0, rmsnorm_f32in(e->hsel, e->res32, m.rows, e->final_w, R, d, s.eps, 1.f, s.logit_scale, elt, st));
+      HFWD(C_NORM, (double)R * d * (4 + es), 0, layer_norm(e->hsel, m.rows, e->final_w, R, s.logit_scale));
       HFWD(R <= 256 ? C_GEMM_S : C_GEMM_L, hb, hf, kge_gemm_bf16(e->logits, e->hsel, e->lm_head, nullptr, R, s.vocab, d, 0, nullptr, 0, st));
-      if (e->want_logits32) HFWD(C_SAMPLE, (double)R * s.vocab * 6, 0, elt16_to_f32(e->logits32, e->logits, (int64_t)R * s.vocab, st));
+      if (s.logit_softcap > 0.f) HFWD(C_SAMPLE, (double)R * s.vocab * (e->want_logits32 ? 8 : 4), 0, softcap_rows(e->want_logits32 ? e->logits32 : nullptr, e->logits, R, s.vocab, e->ld_logits, s.logit_softcap, st));
+      else if (e->want_logits32) HFWD(C_SAMPLE, (double)R * s.vocab * 6, 0, elt16_to_f32(e->logits32, e->logits, (int64_t)R * s.vocab, st));
     } else {
-      HFWD(C_NORM, (double)R * d * (4 + es), 0, rmsnorm_f32in(e->hsel, e->res32, m.rows, e->final_w, R, d, s.eps, 1.f, 1.f, elt, st));
+      HFWD(C_NORM, (double)R * d * (4 + es), 0, layer_norm(e->hsel, m.rows, e->final_w, R, 1.f));
       LinearArgs a;
       a.x = e->hsel; a.ldx = d; a.w = e->lm_head; a.y = e->logits32; a.ldy = s.vocab; a.T = R; a.N = s.vocab; a.K = d;
       a.alpha = s.logit_scale; a.elt = elt; a.out_f32 = true;
       HFWD(R <= 256 ? C_GEMM_S : C_GEMM_L, hb, hf, linear_any(a, st));
+      if (s.logit_softcap > 0.f) HFWD(C_SAMPLE, (double)R * s.vocab * 8, 0, softcap_rows(e->logits32, nullptr, R, s.vocab, 0, s.logit_softcap, st));
       // the samplers read 16-bit logits, rows padded to the 16-byte alignment they ask for
       if (R <= Rm) HFWD(C_SAMPLE, (double)R * s.vocab * 6, 0, logits_to_elt16(e->logits, e->logits32, R, s.vocab, e->ld_logits, false, st));
     }

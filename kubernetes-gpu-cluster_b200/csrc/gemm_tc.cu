@@ -117,6 +117,8 @@ struct GemmParams {
   int m_tiles, n_tiles, splits, kb_total, kb_per_split;
   int rows;                  // gemm_wide_kernel: outputs per tile
   unsigned long long* trace; // phase timestamps, 16 per CTA (tools/gemm_trace.py); null outside that tool
+  int glu = 0;               // gated pair: 0 silu(gate) * up; 1 clamped: g = min(gate, limit), u = clamp(up, +-limit), g * sigmoid(alpha g) * (u + 1)
+  float glu_alpha = 0.f, glu_limit = 0.f;
 };
 
 // epilogue activation of the plain projection: 0 none, 1 relu, 3 exact (erf) gelu; 2 marks the gated pair internally
@@ -161,8 +163,13 @@ __host__ __device__ constexpr int xbuf_bytes(int tokn) { return (tokn + 8) * BLK
 // GATED: the 128 MMA rows of a tile are 64 gate rows (TMEM lanes 0-63) and the matching 64 up rows
 // (lanes 64-127) of a stacked [2f, K] weight; the epilogue emits silu(gate) * up for the 64
 // outputs with vLLM's cast points (vllm:model_executor/layers/activation.py:137-141).
-__device__ __forceinline__ float silu_gate_bf16(float g_acc, float u_acc) {
-  const float g = rbf(g_acc), u = rbf(u_acc);            // the gate_up GEMM output is bf16
+__device__ __forceinline__ float silu_gate_bf16(const GemmParams& p, float g_acc, float u_acc) {
+  float g = rbf(g_acc), u = rbf(u_acc);                  // the gate_up GEMM output is bf16
+  if (p.glu == 1) {                                      // clamped pair with a sigmoid gate: fp32 from the rounded pre-activations
+    g = fminf(g, p.glu_limit);
+    u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
+    return __fdividef(g, 1.0f + __expf(-p.glu_alpha * g)) * (u + 1.0f);
+  }
   const float sg = rbf(__fdividef(g, 1.0f + __expf(-g))); // F.silu rounds to bf16 (fast exp/div: <= 2 ulp in fp32)
   return sg * u;                                          // caller rounds the product once
 }
@@ -493,7 +500,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 float o[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                  if (GATED) o[k] = silu_gate_bf16(a[ci][k], u[ci][k]);
+                  if (GATED) o[k] = silu_gate_bf16(p, a[ci][k], u[ci][k]);
                   else { o[k] = a[ci][k] + bv4[k]; o[k] = apply_act(o[k], p.act); }
                 }
                 bf16* dst = p.y + (int64_t)t * p.N + n0;
@@ -557,7 +564,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
               const int t = t0 + c + col;
               const float gacc = is_up ? hb[(8 + j) * 64 + r64] : __uint_as_float(r[j]);
               const float uacc = is_up ? __uint_as_float(r[8 + j]) : hb[j * 64 + r64];
-              if (t < p.T) p.y[(int64_t)t * p.N + n] = f2bf(silu_gate_bf16(gacc, uacc));
+              if (t < p.T) p.y[(int64_t)t * p.N + n] = f2bf(silu_gate_bf16(p, gacc, uacc));
             }
           }
         }
@@ -616,7 +623,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             if (GATED) {
-              a[k] = silu_gate_bf16(a[k], u[k]);
+              a[k] = silu_gate_bf16(p, a[k], u[k]);
             } else {
               if (p.bias && n0 + k < p.N) a[k] += bf2f(p.bias[n0 + k]);
               a[k] = apply_act(a[k], p.act);
@@ -798,7 +805,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         if (GATED) {
-          o[j] = silu_gate_bf16(a[j], up[j]);
+          o[j] = silu_gate_bf16(p, a[j], up[j]);
         } else {
           const int n = n0 + u * UNIT + j;
           float v = a[j] + ((p.bias && n < p.N) ? bf2f(p.bias[n]) : 0.f);
@@ -1252,10 +1259,12 @@ extern "C" int64_t kge_gemm_workspace_bytes(int T, int N, int K) {
 #define KGE_GEMM_NAME kge_gemm_f16
 #define KGE_GEMM_GATE_NAME kge_gemm_silu_gate_f16
 #define KGE_GEMM_GATE_WS_NAME kge_gemm_silu_gate_ws_f16
+#define KGE_GEMM_GLU_NAME kge_gemm_clamped_glu_f16
 #else
 #define KGE_GEMM_NAME kge_gemm_bf16
 #define KGE_GEMM_GATE_NAME kge_gemm_silu_gate_bf16
 #define KGE_GEMM_GATE_WS_NAME kge_gemm_silu_gate_ws_bf16
+#define KGE_GEMM_GLU_NAME kge_gemm_clamped_glu_bf16
 #endif
 extern "C" int KGE_GEMM_NAME(void* y, const void* x, const void* w, const void* bias, int T, int N, int K,
                              int act, void* workspace, int64_t workspace_bytes, void* stream) {
@@ -1301,8 +1310,8 @@ extern "C" int KGE_GEMM_NAME(void* y, const void* x, const void* w, const void* 
   return dispatch_gemm<false>(g, tw, tx, p, st);
 }
 
-extern "C" int KGE_GEMM_GATE_WS_NAME(void* y, const void* x, const void* w_gate_up, int T, int f, int K, void* workspace,
-                                    int64_t workspace_bytes, void* stream) {
+static int gemm_gated(void* y, const void* x, const void* w_gate_up, int T, int f, int K, int glu, float glu_alpha, float glu_limit, void* workspace,
+                      int64_t workspace_bytes, void* stream) {
   KGE_REQUIRE(y && x && w_gate_up, "kge_gemm_silu_gate_bf16: null pointer");
   KGE_REQUIRE(T >= 0 && f > 0 && K > 0 && K % 8 == 0, "kge_gemm_silu_gate_bf16: K=%d must be a positive multiple of 8", K);
   KGE_REQUIRE(f % 64 == 0, "kge_gemm_silu_gate_bf16: f=%d must be a multiple of 64", f);
@@ -1317,7 +1326,7 @@ extern "C" int KGE_GEMM_GATE_WS_NAME(void* y, const void* x, const void* w_gate_
     GemmPlan gw;
     if (plan_wide(T, f, K, true, gw)) {
       GemmParams p;
-      p.y = (bf16*)y; p.bias = nullptr; p.T = T; p.N = f; p.K = K; p.act = 2;
+      p.y = (bf16*)y; p.bias = nullptr; p.T = T; p.N = f; p.K = K; p.act = 2; p.glu = glu; p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
       p.l2_hints = 0; p.trace = g_gemm_trace; p.ws_count = nullptr; p.ws_part = nullptr;
       p.m_tiles = gw.m_tiles; p.n_tiles = 1; p.splits = gw.splits; p.kb_total = gw.kb_total; p.kb_per_split = gw.kb_per_split;
       CUtensorMap tw, tx;
@@ -1330,7 +1339,7 @@ extern "C" int KGE_GEMM_GATE_WS_NAME(void* y, const void* x, const void* w_gate_
   GemmPlan g = plan_gemm(T, f, K, 64, workspace != nullptr);
   if (g.ws && (workspace_bytes < ws_bytes_of(g) || ((uintptr_t)workspace & 15) != 0)) g = plan_gemm(T, f, K, 64);
   GemmParams p;
-  p.y = (bf16*)y; p.bias = nullptr; p.T = T; p.N = f; p.K = K; p.act = 2;
+  p.y = (bf16*)y; p.bias = nullptr; p.T = T; p.N = f; p.K = K; p.act = 2; p.glu = glu; p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
   p.l2_hints = tunable(TUN_GEMM_L2_HINTS);
   p.trace = g_gemm_trace;
   p.ws_count = g.ws ? (unsigned int*)workspace : nullptr;
@@ -1341,6 +1350,16 @@ extern "C" int KGE_GEMM_GATE_WS_NAME(void* y, const void* x, const void* w_gate_
   if (int rc = make_tmap(&tw, w_gate_up, 2 * (int64_t)f, K, 64)) return rc;     // 64-row boxes: gate half, up half
   if (int rc = make_tmap(&tx, x, T, K, gemm_uses_pair(g) ? 128 : g.tokn)) return rc;
   return dispatch_gemm<true>(g, tw, tx, p, (cudaStream_t)stream);
+}
+
+extern "C" int KGE_GEMM_GATE_WS_NAME(void* y, const void* x, const void* w_gate_up, int T, int f, int K, void* workspace,
+                                    int64_t workspace_bytes, void* stream) {
+  return gemm_gated(y, x, w_gate_up, T, f, K, 0, 0.f, 0.f, workspace, workspace_bytes, stream);
+}
+extern "C" int KGE_GEMM_GLU_NAME(void* y, const void* x, const void* w_gate_up, int T, int f, int K, float alpha, float limit, void* workspace,
+                                int64_t workspace_bytes, void* stream) {
+  KGE_REQUIRE(limit > 0.f, "kge_gemm_clamped_glu_bf16: limit must be positive");
+  return gemm_gated(y, x, w_gate_up, T, f, K, 1, alpha, limit, workspace, workspace_bytes, stream);
 }
 
 extern "C" int KGE_GEMM_GATE_NAME(void* y, const void* x, const void* w_gate_up, int T, int f, int K, void* stream) {

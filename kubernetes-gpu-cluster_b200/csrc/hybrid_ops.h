@@ -1,6 +1,6 @@
 // Launchers of the kernels that layer-list ("hybrid") models add to the library: a shape-agnostic linear layer with
-// grouped / gathered rows, fp32-residual norms, biased chunk-masked paged attention, the gated linear recurrence
-// (RG-LRU), the matrix memory (mLSTM) and the mixture-of-experts router.  Every mechanism takes its sizes and constants
+// grouped / gathered rows, fp32-residual norms, biased chunk-masked paged attention (soft cap, sink logits), rotary
+// positions with a whole-projection norm, the gated linear recurrence (RG-LRU), the matrix memory (mLSTM) and the mixture-of-experts router.  Every mechanism takes its sizes and constants
 // as arguments.  `elt` names the storage type of activations and weights: KGE_ELT_BF16 or KGE_ELT_F32; what the
 // mechanisms compute in 32 bits (softmax, norms, routers, residual sums, recurrent state and everything that enters a
 // recurrence besides projections and short convolutions) is 32-bit in both.
@@ -17,6 +17,8 @@ inline size_t elt_size(int elt) { return elt == KGE_ELT_F32 ? 4 : 2; }
 
 // y[yr(r), n] (+)= alpha * act(scale_r * sum_k x[xr(r), k] * w[n, k] + bias[n])        (w2 == null)
 // y[yr(r), n] (+)= alpha * silu(scale_r * x.w[n]) * (scale_r * x.w2[n])                  (w2 != null: gated pair)
+//   glu == GLU_CLAMPED_SIGMOID: with g = min(scale_r * x.w[n], glu_limit), u = clamp(scale_r * x.w2[n], -glu_limit,
+//   glu_limit) the pair gives alpha * g * sigmoid(glu_alpha * g) * (u + 1)
 // Rows r run over [0, T), or - with group_off - over [group_off[z], group_off[z+1]) for each z < nz, where slice z
 // reads x at column offset z * x_zs, weights at w + z * w_zs (elements), bias at z * b_zs and writes y at column offset
 // z * y_zs.  xrows / yrows (null = identity) gather the input row and scatter the output row; row_scale (null = 1) is
@@ -32,8 +34,10 @@ struct LinearArgs {
   const int32_t* xrows = nullptr; const int32_t* yrows = nullptr;
   const float* row_scale = nullptr;
   int act = ACT_NONE; float alpha = 1.f; bool accumulate = false;
+  int glu = 0; float glu_alpha = 1.702f, glu_limit = 0.f;      // gated pairs: GLU_SILU_MUL or GLU_CLAMPED_SIGMOID
   int elt = KGE_ELT_BF16; bool out_f32 = false;
 };
+enum { GLU_SILU_MUL = 0, GLU_CLAMPED_SIGMOID = 1 };
 int linear_any(const LinearArgs& a, cudaStream_t st);
 
 // res[t, :] = float(table[ids[t], :])
@@ -41,15 +45,27 @@ int embed_f32(float* res, const int32_t* ids, const void* table, int T, int d, i
 // y[r, :] = out_scale * x[rows ? rows[r] : r, :] / sqrt(mean(x^2) + eps) * (offset + w), x fp32, y in elt
 int rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, float out_scale, int elt,
                   cudaStream_t st);
-// res[t, :] += sum_i scale[i] * src[i][t, :]   (up to 4 sources in elt, each [T, d] with its own leading dimension)
-struct CombineArgs { const void* src[4] = {nullptr, nullptr, nullptr, nullptr}; int ld[4] = {0, 0, 0, 0}; float scale[4] = {0, 0, 0, 0}; int n = 0; };
+// the same rows through a layer norm with a weight and no bias: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w, two passes in fp32
+int layernorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float out_scale, int elt, cudaStream_t st);
+// res[t, :] += sum_i scale[i] * rscale_i(t) * src[i][t, :]   (up to 4 sources in elt, each [T, d] with its own leading
+// dimension; rscale_i(t) = rscale[i][t * rs_stride[i]] where a per-row fp32 factor is given, else 1)
+struct CombineArgs {
+  const void* src[4] = {nullptr, nullptr, nullptr, nullptr}; int ld[4] = {0, 0, 0, 0}; float scale[4] = {0, 0, 0, 0};
+  const float* rscale[4] = {nullptr, nullptr, nullptr, nullptr}; int rs_stride[4] = {0, 0, 0, 0};
+  int n = 0;
+};
 int residual_combine(float* res, const CombineArgs& a, int T, int d, int elt, cudaStream_t st);
 // fp32 [R, V] -> 16-bit logits for the samplers (ld_out >= V)
 int logits_to_elt16(void* out, const float* in, int R, int V, int ld_out, bool f16, cudaStream_t st);
 int elt16_to_f32(float* out, const void* in_bf16, int64_t n, cudaStream_t st);
+// soft cap of logits rows, v <- cap * tanh(v / cap) in fp32: on fp32 rows [R, V] in place (l32), and / or on 16-bit rows
+// (l16, row stride ld16) in place; with both given the 16-bit rows are read and the capped value goes to both
+int softcap_rows(float* l32, void* l16, int R, int V, int ld16, float cap, cudaStream_t st);
 
 // Paged attention with a per-head linear distance bias and an optional chunk mask.
-//   score(i, j) = scale * q_i . k_j - slope_h * (i - j),  slope_h = 2^(-bias_span * (h + 1) / H)   (bias_span = 0: no bias)
+//   score(i, j) = cap(scale * q_i . k_j) - slope_h * (i - j),  slope_h = 2^(-bias_span * (h + 1) / H)   (bias_span = 0: no bias),
+//   cap(s) = softcap * tanh(s / softcap) (softcap = 0: s).  With `sinks` (fp32 [H]) the softmax denominator of head h
+//   also holds exp(sinks[h]): a logit without key or value, neither scaled nor capped.
 //   j visible to i iff j <= i and (chunk == 0 or floor(i / chunk) == floor(j / chunk)), positions counted from the
 //   start of the sequence.  Softmax in fp32.  q rows are read from a packed projection buffer (row stride ldq elements,
 //   head h at column h * dim); K cache [num_blocks, G, block_size, dim], V cache [num_blocks, G, block_size, vdim].
@@ -64,13 +80,38 @@ struct AttnBiasArgs {
   int max_q = 0;                           // the longest request's rows in this step (0 = unknown: the per-row kernel runs)
   int num_decode = 0;                      // leading requests that bring one token each: their keys are split over a CTA's warps,
                                            // while requests with many rows give each warp 16 rows of a shared key tile
-  float scale = 1.f, bias_span = 0.f, out_scale = 1.f;
+  float scale = 1.f, bias_span = 0.f, out_scale = 1.f, softcap = 0.f;
+  const float* sinks = nullptr;
   int elt = KGE_ELT_BF16;
 };
 int attn_bias_chunk(const AttnBiasArgs& a, cudaStream_t st);
 // k / v rows of a packed projection buffer -> paged caches (slot = block * block_size + offset, < 0 skips)
 int kv_write_any(const void* k, int ldk, const void* v, int ldv, const int64_t* slots, void* k_cache, void* v_cache, int T, int G,
                  int dim, int vdim, int block_size, int elt, cudaStream_t st);
+
+// Rotary positions for packed q / k projections, with what comes before and after them in one pass over a token's row:
+//   - optional RMS norm over the WHOLE q projection (all heads at once; weight q_norm_w [H * dim]) and over the whole
+//     k projection (k_norm_w [G * dim]), in fp32: x / sqrt(mean(x^2) + eps) * w;
+//   - rotation of the first rot_dims dimensions of every head in interleaved pairs (2i, 2i + 1):
+//     (u, v) -> mult * (u cos a - v sin a, v cos a + u sin a), a = position * freq[i]; the angle is formed and reduced
+//     in double precision, freq [rot_dims / 2] comes from rotary_frequencies();
+//   - q is written back in place, the rotated k goes to the paged key cache, and the value cache receives either the
+//     rows of `v` or (v == null) the key projection as it came in, before norm and rotation.
+// Caches as in kv_write_any: [num_blocks, G, block_size, dim]; slot < 0 skips the cache writes.
+struct RotaryArgs {
+  void* q = nullptr; int ldq = 0; const void* k = nullptr; int ldk = 0; const void* v = nullptr; int ldv = 0;
+  const void* q_norm_w = nullptr; const void* k_norm_w = nullptr; float eps = 1e-5f;
+  const double* freq = nullptr; float mult = 1.f; int rot_dims = 0;
+  const int32_t* positions = nullptr; const int64_t* slots = nullptr;
+  void* k_cache = nullptr; void* v_cache = nullptr;
+  int T = 0, H = 0, G = 0, dim = 0, vdim = 0, block_size = 0;
+  int elt = KGE_ELT_BF16;
+};
+int rotary_norm_kvwrite(const RotaryArgs& a, cudaStream_t st);
+// freq[i] = base^(-2i / dims), i < dims / 2; with YaRN scaling (factor > 0): ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+// between lo = max(floor(c(fast)), 0) and hi = min(ceil(c(slow)), dims - 1), c(t) = dims * ln(original / (2 pi t)) / (2 ln base);
+// freq_i <- freq_i / factor * ramp_i + freq_i * (1 - ramp_i) and *mult = 0.1 ln(factor) + 1 (else 1).  Host only.
+void rotary_frequencies(int dims, double base, double factor, double original, double fast, double slow, double* freq, float* mult);
 
 // Gated linear recurrence (RG-LRU).  yx [T, 2 * width]: the y branch's pre-activation, then the x branch (biases in).
 //   u = causal per-channel conv of x (taps weights per channel, last tap on the current token; inputs before position 0
@@ -114,19 +155,20 @@ struct MlstmArgs {
 int mlstm_step(const MlstmArgs& a, cudaStream_t st);
 inline int64_t mlstm_state_floats(int H, int dim, int vdim) { return (int64_t)H * ((int64_t)dim * vdim + dim + 1); }
 
-// Mixture-of-experts routing: logits z = W_router h in fp32, scores sigmoid(z) (score_fn 0) or softmax(z) (1), the `top`
-// largest chosen (ties to the lower index), weights = scores, renormalised to sum 1 if renorm.  Produces for every
+// Mixture-of-experts routing: logits z = W_router h (+ b_router) in fp32, scores sigmoid(z) (score_fn 0) or softmax(z) (1),
+// the `top` largest chosen (ties to the lower index), weights = scores, renormalised to sum 1 if renorm; score_fn 2:
+// the `top` largest LOGITS are chosen and the weights are the softmax over the chosen logits only.  Produces for every
 // expert the list of (token, choice) pairs routed to it: group_off [E + 1], perm_token [T * top] (the token row of
 // every permuted row), perm_weight [T * top], perm_dest [T * top] (row t * top + choice of the output buffer).
 struct MoeRouteArgs {
-  const void* h = nullptr; int ldh = 0; const void* w_router = nullptr;
+  const void* h = nullptr; int ldh = 0; const void* w_router = nullptr; const void* b_router = nullptr;
   int T = 0, d = 0, E = 0, top = 1, score_fn = 0; bool renorm = false;
   int32_t* group_off = nullptr; int32_t* perm_token = nullptr; float* perm_weight = nullptr; int32_t* perm_dest = nullptr;
   int32_t* choice_expert = nullptr; float* choice_weight = nullptr;     // scratch [T * top] each
   int elt = KGE_ELT_BF16;
 };
 int moe_route(const MoeRouteArgs& a, cudaStream_t st);
-// routed rows made contiguous per expert: xperm[p, :] = bf16(perm_weight[p] * h[perm_token[p], :]); and back: out[perm_dest[p], :] = operm[p, :]
+// routed rows made contiguous per expert: xperm[p, :] = bf16(perm_weight[p] * h[perm_token[p], :]) (null weights: 1); and back: out[perm_dest[p], :] = operm[p, :]
 int moe_gather_rows(void* xperm, const void* h, int ldh, const int32_t* perm_token, const float* perm_weight, int np, int d, cudaStream_t st);
 int moe_scatter_rows(void* out, const void* operm, const int32_t* perm_dest, int np, int d, cudaStream_t st);
 

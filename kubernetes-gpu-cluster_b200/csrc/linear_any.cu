@@ -25,6 +25,16 @@ __device__ __forceinline__ float act_apply(int act, float v) {
   }
 }
 
+// the gated pair of two pre-activations (row scale applied)
+__device__ __forceinline__ float glu_apply(const LinearArgs& a, float g, float u) {
+  if (a.glu == GLU_CLAMPED_SIGMOID) {
+    g = fminf(g, a.glu_limit);
+    u = fminf(fmaxf(u, -a.glu_limit), a.glu_limit);
+    return g / (1.f + expf(-a.glu_alpha * g)) * (u + 1.f);
+  }
+  return act_apply(ACT_SILU, g) * u;
+}
+
 constexpr int LBM = 64, LBN = 64, LBK = 16;
 
 template <typename E, typename O, bool DUAL>
@@ -88,7 +98,7 @@ __global__ void __launch_bounds__(256) linear_any_kernel(LinearArgs a) {
       const int n = n0 + tx * 4 + j;
       if (n >= a.N) continue;
       float v;
-      if (DUAL) v = act_apply(ACT_SILU, s * acc[i][j]) * (s * acc2[i][j]);
+      if (DUAL) v = glu_apply(a, s * acc[i][j], s * acc2[i][j]);
       else v = act_apply(a.act, s * acc[i][j] + (bias ? ldf(bias + n) : 0.f));
       v *= a.alpha;
       O* dst = y + (int64_t)yr * a.ldy + n;
@@ -214,7 +224,7 @@ __global__ void __launch_bounds__(256) linear_mma_kernel(LinearArgs a) {
           if (n >= a.N) continue;
           const float s1 = acc[i][j][hh * 2 + c];
           float v;
-          if (DUAL) v = act_apply(ACT_SILU, sc * s1) * (sc * acc2[i][j][hh * 2 + c]);
+          if (DUAL) v = glu_apply(a, sc * s1, sc * acc2[i][j][hh * 2 + c]);
           else v = act_apply(a.act, sc * s1 + (bias ? ldf(bias + n) : 0.f));
           v *= a.alpha;
           O* dst = y + (int64_t)yr * a.ldy + n;
@@ -283,6 +293,33 @@ int rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, i
   return 0;
 }
 
+// weight-only layer norm of an fp32 row: mean first, then the mean of the squared deviations (no cancellation)
+template <typename E>
+__global__ void layernorm_f32in_kernel(E* y, const float* x, const int32_t* rows, const E* w, int d, float eps, float out_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const float* src = x + (int64_t)(rows ? rows[r] : r) * d;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) s += src[c];
+  const float mean = block_sum(s, red) / (float)d;
+  __syncthreads();
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) { const float v = src[c] - mean; ss = fmaf(v, v, ss); }
+  ss = block_sum(ss, red);
+  const float inv = out_scale / sqrtf(ss / (float)d + eps);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) stf(y + (int64_t)r * d + c, (src[c] - mean) * inv * ldf(w + c));
+}
+int layernorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float out_scale, int elt, cudaStream_t st) {
+  if (R <= 0) return 0;
+  cudaError_t ce = elt == KGE_ELT_F32
+      ? launch_pdl(layernorm_f32in_kernel<float>, dim3(R), dim3(256), 0, st, (float*)y, x, rows, (const float*)w, d, eps, out_scale)
+      : launch_pdl(layernorm_f32in_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, st, (__nv_bfloat16*)y, x, rows, (const __nv_bfloat16*)w, d, eps, out_scale);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
 template <typename E>
 __global__ void residual_combine_kernel(float* res, CombineArgs a, int64_t n, int d) {
   pdl_launch_dependents();
@@ -290,7 +327,10 @@ __global__ void residual_combine_kernel(float* res, CombineArgs a, int64_t n, in
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / d; const int c = (int)(i % d);
     float s = 0.f;
-    for (int k = 0; k < a.n; ++k) s = fmaf(a.scale[k], ldf((const E*)a.src[k] + t * a.ld[k] + c), s);
+    for (int k = 0; k < a.n; ++k) {
+      const float f = a.rscale[k] ? a.scale[k] * a.rscale[k][t * a.rs_stride[k]] : a.scale[k];
+      s = fmaf(f, ldf((const E*)a.src[k] + t * a.ld[k] + c), s);
+    }
     res[i] += s;
   }
 }
@@ -328,6 +368,26 @@ __global__ void elt16_to_f32_kernel(float* out, const __nv_bfloat16* in, int64_t
 int elt16_to_f32(float* out, const void* in_bf16, int64_t n, cudaStream_t st) {
   if (n <= 0) return 0;
   KGE_CUDA_OK(launch_pdl(elt16_to_f32_kernel, dim3((unsigned)std::min<int64_t>((n + 255) / 256, 148 * 8)), dim3(256), 0, st, out, (const __nv_bfloat16*)in_bf16, n));
+  return 0;
+}
+
+
+__device__ __forceinline__ float softcap_f(float v, float cap) { return cap * tanhf(v / cap); }
+__global__ void softcap_rows_kernel(float* l32, __nv_bfloat16* l16, int R, int V, int ld16, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t n = (int64_t)R * V;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / V; const int c = (int)(i % V);
+    const float v = softcap_f(l16 ? __bfloat162float(l16[r * ld16 + c]) : l32[i], cap);
+    if (l32) l32[i] = v;
+    if (l16) l16[r * ld16 + c] = __float2bfloat16_rn(v);
+  }
+}
+int softcap_rows(float* l32, void* l16, int R, int V, int ld16, float cap, cudaStream_t st) {
+  if (R <= 0 || cap <= 0.f) return 0;
+  const int grid = (int)std::min<int64_t>(((int64_t)R * V + 255) / 256, 148 * 8);
+  KGE_CUDA_OK(launch_pdl(softcap_rows_kernel, dim3(grid), dim3(256), 0, st, l32, (__nv_bfloat16*)l16, R, V, ld16, cap));
   return 0;
 }
 

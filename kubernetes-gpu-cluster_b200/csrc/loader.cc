@@ -30,6 +30,26 @@ static bool read_file(const std::string& path, std::string* out) {
   return true;
 }
 
+// the feed-forward entry of a layer ('mlp': null for none)
+static bool parse_hybrid_mlp(const Json& l, HybridLayerSpec* hp, std::string* err) {
+  HybridLayerSpec& h = *hp;
+  const Json* f = l.get("mlp");
+  if (f && f->is_obj()) {
+    const std::string kind = f->str_or("kind", "");
+    if (kind == "dense") { h.mlp = HybridLayerSpec::DENSE; h.ff = (int)f->int_or("ff", 0); if (h.ff <= 0) { *err = "config.json: dense mlp without ff"; return false; } }
+    else if (kind == "moe") {
+      h.mlp = HybridLayerSpec::MOE;
+      const Json *ex = f->get("expert"), *ro = f->get("router"), *sh = f->get("shared");
+      if (!ex || !ro) { *err = "config.json: moe mlp needs 'expert' and 'router'"; return false; }
+      h.expert_ff = (int)ex->int_or("ff", 0); h.experts = (int)ro->int_or("experts", 0); h.top = (int)ro->int_or("top", 1);
+      if (sh && sh->is_obj()) { h.shared_ff = (int)sh->int_or("ff", 0); h.shared_limit = (float)sh->num_or("limit", 0.0); }
+      h.expert_limit = (float)ex->num_or("limit", 0.0);
+      if (h.expert_ff <= 0 || h.experts <= 0 || h.top <= 0 || h.top > h.experts) { *err = "config.json: bad moe sizes"; return false; }
+    } else { *err = "config.json: unknown mlp kind '" + kind + "'"; return false; }
+  }
+  return true;
+}
+
 // Layer-list models: config.json carries "architecture" and a "layers" array instead of HF's flat sizes.
 static bool parse_hybrid(const Json& j, ModelSpec* s, std::string* err) {
   s->model_type = "safupel";
@@ -66,18 +86,70 @@ static bool parse_hybrid(const Json& j, ModelSpec* s, std::string* err) {
       if (h.heads <= 0 || h.kv_heads <= 0 || h.heads % h.kv_heads || h.dim <= 0 || h.vdim <= 0 || h.m_heads <= 0 || h.m_dim <= 0 ||
           h.m_vdim <= 0 || h.gate_cap <= 0.f || h.chunk < 0) { *err = "config.json: bad parallel-mixer sizes"; return false; }
     } else { *err = "config.json: unknown layer type '" + type + "' (rglru, parallel)"; return false; }
-    const Json* f = l.get("mlp");
-    if (f && f->is_obj()) {
-      const std::string kind = f->str_or("kind", "");
-      if (kind == "dense") { h.mlp = HybridLayerSpec::DENSE; h.ff = (int)f->int_or("ff", 0); if (h.ff <= 0) { *err = "config.json: dense mlp without ff"; return false; } }
-      else if (kind == "moe") {
-        h.mlp = HybridLayerSpec::MOE;
-        const Json *ex = f->get("expert"), *ro = f->get("router"), *sh = f->get("shared");
-        if (!ex || !ro) { *err = "config.json: moe mlp needs 'expert' and 'router'"; return false; }
-        h.expert_ff = (int)ex->int_or("ff", 0); h.experts = (int)ro->int_or("experts", 0); h.top = (int)ro->int_or("top", 1);
-        if (sh && sh->is_obj()) h.shared_ff = (int)sh->int_or("ff", 0);
-        if (h.expert_ff <= 0 || h.experts <= 0 || h.top <= 0 || h.top > h.experts) { *err = "config.json: bad moe sizes"; return false; }
-      } else { *err = "config.json: unknown mlp kind '" + kind + "'"; return false; }
+    if (!parse_hybrid_mlp(l, &h, err)) return false;
+    s->hybrid.push_back(h);
+  }
+  s->L = (int)s->hybrid.size();
+  if (s->vocab <= 0 || s->d <= 0) { *err = "config.json misses a required size"; return false; }
+  return true;
+}
+
+// Girolorn: a layer list of attention mixers (soft-capped scores, a sink logit per head, RMS norm over the whole q / k
+// projections, values = the key projection, interleaved partial rotary positions with YaRN scaling) and mixtures of
+// experts (softmax over the chosen logits, clamped gated units, a gated shared expert); weight-only layer norms before
+// the mixer and before the feed-forward; layers may run with another layer's tensors; soft-capped logits.
+static bool parse_girolorn(const Json& j, ModelSpec* s, std::string* err) {
+  s->model_type = "girolorn";
+  s->vocab = (int)j.int_or("vocab", 0);
+  s->d = (int)j.int_or("width", 0);
+  s->logit_softcap = (float)j.num_or("logit_softcap", 0.0);
+  if (const Json* n = j.get("norm")) s->eps = (float)n->num_or("eps", 1e-5);
+  s->hyb_prenorm_pair = s->hyb_layernorm = true;
+  s->max_pos = 1 << 20;                 // rotary angles are computed from the position: no table bounds them
+  s->torch_dtype = "bfloat16";
+  s->bos = (int)j.int_or("bos_token_id", -1);
+  s->eos = (int)j.int_or("eos_token_id", -1);
+  const Json* ls = j.get("layers");
+  if (!ls || !ls->is_arr() || ls->arr.empty()) { *err = "config.json: 'layers' must be a non-empty array"; return false; }
+  for (const Json& l : ls->arr) {
+    HybridLayerSpec h;
+    const std::string type = l.str_or("type", "");
+    const Json* m = l.get("mixer");
+    if (!m || !m->is_obj()) { *err = "config.json: a layer has no 'mixer'"; return false; }
+    if (type != "attention") { *err = "config.json: unknown layer type '" + type + "' (attention)"; return false; }
+    h.mixer = HybridLayerSpec::ATTENTION;
+    h.heads = (int)m->int_or("heads", 0); h.kv_heads = (int)m->int_or("kv_heads", h.heads);
+    h.dim = (int)m->int_or("dim", 0); h.vdim = (int)m->int_or("vdim", h.dim);
+    h.scale = (float)m->num_or("scale", 1.0);
+    h.softcap = (float)m->num_or("softcap", 0.0);
+    h.sink = h.qk_norm = h.v_from_k = true;
+    if (const Json* r = m->get("rot")) {
+      if (r->is_obj()) {
+        h.rot_dims = (int)r->int_or("dims", 0); h.rot_base = r->num_or("base", 10000.0);
+        const Json* sc = r->get("scaling");
+        if (sc && sc->is_obj()) {
+          h.yarn_factor = sc->num_or("factor", 0.0); h.yarn_original = sc->num_or("original", 0.0);
+          h.yarn_fast = sc->num_or("fast", 32.0); h.yarn_slow = sc->num_or("slow", 1.0);
+          if (h.yarn_factor <= 0.0 || h.yarn_original <= 0.0 || h.yarn_fast <= 0.0 || h.yarn_slow <= 0.0) { *err = "config.json: bad rotary scaling"; return false; }
+        }
+      }
+    }
+    if (h.heads <= 0 || h.kv_heads <= 0 || h.heads % h.kv_heads || h.dim <= 0 || h.vdim != h.dim || h.rot_dims < 0 || h.rot_dims > h.dim ||
+        h.rot_dims % 2 || h.rot_base <= 0.0 || h.softcap < 0.f) { *err = "config.json: bad attention sizes (values are the keys: vdim = dim)"; return false; }
+    if (!parse_hybrid_mlp(l, &h, err)) return false;
+    if (h.mlp == HybridLayerSpec::DENSE) { *err = "config.json: this architecture has no dense mlp"; return false; }
+    if (h.mlp == HybridLayerSpec::MOE) {
+      h.route = HybridLayerSpec::ROUTE_SOFTMAX_TOP; h.router_bias = true; h.glu = HybridLayerSpec::GLU_CLAMPED; h.shared_gate = h.shared_ff > 0;
+      if (h.expert_limit <= 0.f || (h.shared_ff > 0 && h.shared_limit <= 0.f)) { *err = "config.json: an expert needs a positive 'limit'"; return false; }
+    }
+    if (const Json* wo = l.get("weights_of")) {
+      if (!wo->is_num()) { *err = "config.json: 'weights_of' must be a layer index"; return false; }
+      h.weights_of = (int)wo->as_i64();
+      const int self = (int)s->hybrid.size();
+      if (h.weights_of < 0 || h.weights_of >= self || s->hybrid[h.weights_of].weights_of >= 0) { *err = "config.json: 'weights_of' must name an earlier layer with tensors of its own"; return false; }
+      const HybridLayerSpec& o = s->hybrid[h.weights_of];
+      if (o.heads != h.heads || o.kv_heads != h.kv_heads || o.dim != h.dim || o.mlp != h.mlp || o.experts != h.experts || o.expert_ff != h.expert_ff ||
+          o.shared_ff != h.shared_ff) { *err = "config.json: a layer with 'weights_of' must have that layer's sizes"; return false; }
     }
     s->hybrid.push_back(h);
   }
@@ -88,6 +160,7 @@ static bool parse_hybrid(const Json& j, ModelSpec* s, std::string* err) {
 
 static bool parse_config(const Json& j, ModelSpec* s, std::string* err) {
   if (j.str_or("architecture", "") == "Safupel") return parse_hybrid(j, s, err);
+  if (j.str_or("architecture", "") == "Girolorn") return parse_girolorn(j, s, err);
   s->model_type = j.str_or("model_type", "");
   s->vocab = (int)j.int_or("vocab_size", 0);
   s->d = (int)j.int_or("hidden_size", 0);
@@ -314,18 +387,22 @@ extern "C" int kge_model_spec_json(const kge_model_dir* m, char* out, int cap) {
   if (s.is_hybrid()) {
     std::string j = "{\"model_type\":\"" + s.model_type + "\",\"vocab\":" + std::to_string(s.vocab) + ",\"d\":" + std::to_string(s.d) +
                     ",\"L\":" + std::to_string(s.L) + ",\"has_weights\":" + (m->md.has_weights() ? "true" : "false") + ",\"layers\":[";
-    char buf[512];
+    char buf[1024];
     for (size_t i = 0; i < s.hybrid.size(); ++i) {
       const kge::HybridLayerSpec& h = s.hybrid[i];
       snprintf(buf, sizeof buf,
                "%s{\"mixer\":%d,\"width\":%d,\"blocks\":%d,\"conv\":%d,\"heads\":%d,\"kv_heads\":%d,\"dim\":%d,\"vdim\":%d,\"chunk\":%d,"
                "\"scale\":%.9g,\"left_scale\":%.9g,\"right_scale\":%.9g,\"m_heads\":%d,\"m_dim\":%d,\"m_vdim\":%d,\"gate_cap\":%.9g,"
-               "\"mlp\":%d,\"ff\":%d,\"experts\":%d,\"top\":%d,\"expert_ff\":%d,\"shared_ff\":%d}",
+               "\"mlp\":%d,\"ff\":%d,\"experts\":%d,\"top\":%d,\"expert_ff\":%d,\"shared_ff\":%d,\"softcap\":%.9g,\"rot_dims\":%d,\"rot_base\":%.17g,"
+               "\"yarn_factor\":%.17g,\"yarn_original\":%.17g,\"yarn_fast\":%.17g,\"yarn_slow\":%.17g,\"route\":%d,\"glu\":%d,\"expert_limit\":%.9g,"
+               "\"shared_limit\":%.9g,\"weights_of\":%d}",
                i ? "," : "", h.mixer, h.width, h.blocks, h.conv, h.heads, h.kv_heads, h.dim, h.vdim, h.chunk, (double)h.scale, (double)h.left_scale,
-               (double)h.right_scale, h.m_heads, h.m_dim, h.m_vdim, (double)h.gate_cap, h.mlp, h.ff, h.experts, h.top, h.expert_ff, h.shared_ff);
+               (double)h.right_scale, h.m_heads, h.m_dim, h.m_vdim, (double)h.gate_cap, h.mlp, h.ff, h.experts, h.top, h.expert_ff, h.shared_ff,
+               (double)h.softcap, h.rot_dims, h.rot_base, h.yarn_factor, h.yarn_original, h.yarn_fast, h.yarn_slow, h.route, h.glu, (double)h.expert_limit,
+               (double)h.shared_limit, h.weights_of);
       j += buf;
     }
-    snprintf(buf, sizeof buf, "],\"eps\":%.9g,\"logit_scale\":%.9g}", (double)s.eps, (double)s.logit_scale);
+    snprintf(buf, sizeof buf, "],\"eps\":%.9g,\"logit_scale\":%.9g,\"logit_softcap\":%.9g}", (double)s.eps, (double)s.logit_scale, (double)s.logit_softcap);
     j += buf;
     KGE_REQUIRE((int)j.size() < cap, "kge_model_spec_json: buffer of %d bytes too small", cap);
     memcpy(out, j.c_str(), j.size() + 1);

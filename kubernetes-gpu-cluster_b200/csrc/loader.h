@@ -12,7 +12,7 @@ namespace kge {
 // One layer of a layer-list ("hybrid") model: which token mixer it has, that mixer's sizes and constants, and its
 // feed-forward.  Every number comes from config.json; the kernels take them as parameters.
 struct HybridLayerSpec {
-  enum Mixer { RGLRU = 0, PARALLEL = 1 };
+  enum Mixer { RGLRU = 0, PARALLEL = 1, ATTENTION = 2 };
   enum Mlp { NONE = 0, DENSE = 1, MOE = 2 };
   int mixer = RGLRU;
   // gated linear recurrence (RG-LRU): two branches of `width`, gates block-diagonal in `blocks` parts, causal conv of `conv` taps
@@ -24,17 +24,44 @@ struct HybridLayerSpec {
   // matrix-memory side (mLSTM): heads x (dim x vdim) state, gate pre-activations soft-capped at gate_cap
   int m_heads = 0, m_dim = 0, m_vdim = 0;
   float gate_cap = 0.f, right_scale = 1.f;
+  // attention alone (ATTENTION; heads / kv_heads / dim / vdim / scale as above): scores soft-capped at `softcap` (0 = not),
+  // a learned per-head sink logit in the softmax denominator, RMS norm of the whole q and k projections (before they are
+  // split into heads), values taken from the key projection as it leaves the matrix product (no value matrix), rotary
+  // positions on the first rot_dims dimensions of every head in interleaved pairs, with YaRN frequency scaling
+  // (yarn_factor 0 = plain frequencies)
+  float softcap = 0.f;
+  bool sink = false, qk_norm = false, v_from_k = false;
+  int rot_dims = 0;
+  double rot_base = 10000.0, yarn_factor = 0.0, yarn_original = 0.0, yarn_fast = 32.0, yarn_slow = 1.0;
   // feed-forward
   int mlp = NONE;
   int ff = 0;                                    // dense
   int experts = 0, top = 0, expert_ff = 0, shared_ff = 0;   // mixture of experts (+ an always-on shared expert if shared_ff > 0)
+  // how the experts are chosen and weighed: ROUTE_SIGMOID_IN - sigmoid scores, the weight multiplies the expert's input;
+  // ROUTE_SOFTMAX_TOP - the largest logits (router bias added), softmax over the chosen logits only, the weight multiplies
+  // the expert's output
+  enum Route { ROUTE_SIGMOID_IN = 0, ROUTE_SOFTMAX_TOP = 1 };
+  int route = ROUTE_SIGMOID_IN;
+  bool router_bias = false;
+  // the experts' gated unit: GLU_SILU - silu(gate) * up; GLU_CLAMPED - g = min(gate, limit), u = clamp(up, -limit, limit),
+  // g * sigmoid(1.702 g) * (u + 1)
+  enum Glu { GLU_SILU = 0, GLU_CLAMPED = 1 };
+  int glu = GLU_SILU;
+  float expert_limit = 0.f, shared_limit = 0.f;
+  bool shared_gate = false;                      // the shared expert's output is multiplied by sigmoid(w_sg . h), one number per token
+  int weights_of = -1;                           // >= 0: this layer owns no tensors and runs with that layer's (cache and state stay its own)
 };
 
 struct ModelSpec {
-  std::string model_type;       // "opt" | "llama" | "qwen2" | "qwen3" | "safupel"
+  std::string model_type;       // "opt" | "llama" | "qwen2" | "qwen3" | "safupel" | "girolorn"
   // layer-list models (config.json "architecture"): per-layer descriptions and the multiplier of the logits
   std::vector<HybridLayerSpec> hybrid;
   float logit_scale = 1.f;
+  float logit_softcap = 0.f;    // > 0: logits <- cap * tanh(logits / cap)
+  // norms of a layer-list model: one RMS norm (weight applied as 1 + w) that mixer and feed-forward both read, or
+  // (hyb_prenorm_pair) a norm before the mixer and, after the mixer's sum, another before the feed-forward;
+  // hyb_layernorm: mean-centred layer norm with a weight and no bias instead of the RMS norm
+  bool hyb_prenorm_pair = false, hyb_layernorm = false;
   bool is_hybrid() const { return !hybrid.empty(); }
   bool qkv_bias = false;        // qwen2: q/k/v projections carry a bias
   bool qk_norm = false;         // qwen3: RMSNorm over head_dim on q and k, per head, before RoPE

@@ -1,4 +1,5 @@
-// Mixture-of-experts routing: fp32 router logits, sigmoid or softmax scores, top-k choice, and the grouping of
+// Mixture-of-experts routing: fp32 router logits (optional bias), sigmoid or softmax scores or the raw logits with a
+// softmax over the chosen ones, top-k choice, and the grouping of
 // (token, choice) pairs by expert that the grouped linear layer consumes.  Which rows an expert gets is all that the
 // grouping decides: a pair's result does not depend on its place in the group, and the pairs of a token are summed in
 // choice order afterwards, so the routing order never shows in the output.
@@ -23,13 +24,13 @@ __global__ void __launch_bounds__(256) moe_score_kernel(MoeRouteArgs a) {
 #pragma unroll 8
     for (int k = lane; k < a.d; k += 32) acc = fmaf(ldf(h + k), ldf(w + k), acc);
     acc = warp_sum(acc);
-    if (lane == 0) sc[e] = acc;
+    if (lane == 0) sc[e] = a.b_router ? acc + ldf((const E*)a.b_router + e) : acc;
   }
   __syncthreads();
   if (warp != 0) return;
   if (a.score_fn == 0) {
     for (int e = lane; e < a.E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
-  } else {
+  } else if (a.score_fn == 1) {
     float mx = -INFINITY;
     for (int e = lane; e < a.E; e += 32) mx = fmaxf(mx, sc[e]);
     mx = warp_max(mx);
@@ -54,7 +55,12 @@ __global__ void __launch_bounds__(256) moe_score_kernel(MoeRouteArgs a) {
       a.choice_weight[(int64_t)t * a.top + k] = bv;
       total += bv;
     }
-    if (a.renorm) for (int k = 0; k < a.top; ++k) a.choice_weight[(int64_t)t * a.top + k] /= total;
+    if (a.score_fn == 2) {          // softmax over the chosen logits only (the first choice holds the largest)
+      const float mx = a.choice_weight[(int64_t)t * a.top];
+      total = 0.f;
+      for (int k = 0; k < a.top; ++k) { const float p = expf(a.choice_weight[(int64_t)t * a.top + k] - mx); a.choice_weight[(int64_t)t * a.top + k] = p; total += p; }
+      for (int k = 0; k < a.top; ++k) a.choice_weight[(int64_t)t * a.top + k] /= total;
+    } else if (a.renorm) for (int k = 0; k < a.top; ++k) a.choice_weight[(int64_t)t * a.top + k] /= total;
   }
 }
 
@@ -87,7 +93,7 @@ __global__ void moe_gather_rows_kernel(__nv_bfloat16* xperm, const __nv_bfloat16
   pdl_wait();
   const int p = blockIdx.x;
   const __nv_bfloat16* src = h + (int64_t)tok[p] * ldh;
-  const float s = w[p];
+  const float s = w ? w[p] : 1.f;
   for (int c = threadIdx.x; c < d; c += blockDim.x) xperm[(int64_t)p * d + c] = __float2bfloat16_rn(s * __bfloat162float(src[c]));
 }
 __global__ void moe_scatter_rows_kernel(__nv_bfloat16* out, const __nv_bfloat16* operm, const int32_t* dest, int d) {
