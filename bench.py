@@ -2,7 +2,7 @@
 """Headline benchmark: output tokens/s at fixed concurrency (BASELINE.json `metric`).
 
   python bench.py --gpus N --steps K --warmup W [--workload c3|c2|c1] [--impl ours|reference]
-  python bench.py --designs        (the layer-list design beside a Llama of equal size; one JSON line per size)
+  python bench.py --designs [safupel|girolorn]   (a layer-list design beside a Llama of equal size; one JSON line per size)
 
 A "step" is one whole job of the workload: every request prefilled (2k-token prompts, 8192 tokens
 per engine step as the continuous-batching scheduler cuts them) and decoded greedily to its output length.

@@ -323,7 +323,8 @@ int attn_decode_splits(int B, int KV, int max_seq_len);
 bool decode_tma_supported(int B, int KV, int bs);          // attn_decode_tma.cu
 int paged_attn_decode_tma(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc, const int32_t* bt, int max_blocks,
                           const int32_t* sl, const int32_t* qsl, int B, int H, int KV, int hd, int bs, int ns, float scale_log2,
-                          float* part_o, float* part_ml, void* ws, int64_t ws_bytes, int max_seq_len, cudaStream_t st);
+                          float* part_o, float* part_ml, void* ws, int64_t ws_bytes, int max_seq_len, float cap_in2, float cap_log2,
+                          const float* sinks, cudaStream_t st);
 static int decode_splits(int B, int KV, int max_seq_len) { return attn_decode_splits(B, KV, max_seq_len); }
 // Split-KV factor of a decode launch; also part of the key of the engine's captured decode graphs.
 int attn_decode_splits(int B, int KV, int max_seq_len) {
@@ -354,14 +355,16 @@ template <int HD>
 static int launch_attn(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc,
                        const int32_t* bt, int max_blocks, const int32_t* sl, const int32_t* qsl, int B,
                        int max_q_len, int max_seq_len, int H, int KV, int bs, float scale, void* ws,
-                       int64_t ws_bytes, cudaStream_t st) {
+                       int64_t ws_bytes, float softcap, const float* sinks, cudaStream_t st) {
   const float sl2 = scale * kLog2e;
+  const bool extras = softcap > 0.f || sinks;      // soft cap / sink logits: the TMA-staged kernels have them
+  const float cap_in2 = softcap > 0.f ? 2.f * kLog2e * scale / softcap : 0.f, cap_log2 = softcap * kLog2e;
   int bs_shift = 0;
   while ((1 << bs_shift) < bs) ++bs_shift;
   const int G = H / KV;
   if (max_q_len == 1 && G <= 16) {
     const int ns = decode_splits(B, KV, max_seq_len);
-    if (ns > 1 && ns <= 8 && tunable(TUN_ATTN_CLUSTER_MERGE)) {
+    if (ns > 1 && ns <= 8 && tunable(TUN_ATTN_CLUSTER_MERGE) && !extras) {
       // opt-in: split-KV CTAs of one (request, kv head) as a cluster, merged over DSMEM - no workspace and one
       // kernel, but measured SLOWER than the merge kernel behind programmatic dependent launch (C3 decode step
       // 7.64 vs 7.38 ms, profiles/r01_knob_sweep.md): cluster co-scheduling costs more than the extra launch
@@ -392,7 +395,8 @@ static int launch_attn(bf16* out, const bf16* q, int q_stride, const bf16* kc, c
     // boxes are large enough and TMA wins, 96 us at 64)
     if (tunable(TUN_ATTN_TMA) && bs >= 32 && decode_tma_supported(B, KV, bs))
       return paged_attn_decode_tma(out, q, q_stride, kc, vc, bt, max_blocks, sl, qsl, B, H, KV, HD, bs, ns, sl2, po, pml, ws, ws_bytes,
-                                   max_seq_len, st);
+                                   max_seq_len, cap_in2, cap_log2, sinks, st);
+    KGE_REQUIRE(!extras, "paged attention: a soft cap or sink logits need the TMA-staged decode kernel (blocks of 32 tokens or more)");
     auto kern = attn_decode_kernel<HD, kDecodeStages, false>;
     KGE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<HD>()));
     KGE_CUDA_OK(launch_pdl(kern, dim3(ns, KV, B), dim3(128), decode_smem<HD>(), st, out, po, pml, q, q_stride, kc, vc, bt,
@@ -422,11 +426,14 @@ extern "C" int64_t kge_attn_workspace_bytes(int B, int H, int hd, int max_seq_le
 
 #endif
 
-extern "C" int KGE_API(kge_paged_attn)(void* out, const void* q, int q_stride, const void* k_cache,
-                              const void* v_cache, const int32_t* block_table, int max_blocks_per_seq,
-                              const int32_t* seq_lens, const int32_t* query_start_loc, int B, int T,
-                              int max_q_len, int max_seq_len, int H, int KV, int hd, int block_size,
-                              float scale, void* workspace, int64_t workspace_bytes, void* stream) {
+namespace kge {
+inline namespace KGE_ELT_NS {
+// kge_paged_attn with the extras of layer-list attention mixers: scores soft-capped at `softcap` (0 = not) and a sink
+// logit per head in the softmax denominator (`sinks`, fp32 [H], or null)
+int paged_attn_extras(void* out, const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                      int max_blocks_per_seq, const int32_t* seq_lens, const int32_t* query_start_loc, int B, int T, int max_q_len,
+                      int max_seq_len, int H, int KV, int hd, int block_size, float scale, float softcap, const float* sinks, void* workspace,
+                      int64_t workspace_bytes, void* stream) {
   KGE_REQUIRE(out && q && k_cache && v_cache && block_table && seq_lens && query_start_loc,
               "kge_paged_attn: null pointer");
   KGE_REQUIRE(H > 0 && KV > 0 && H % KV == 0, "kge_paged_attn: H=%d must be a multiple of KV=%d", H, KV);
@@ -438,17 +445,33 @@ extern "C" int KGE_API(kge_paged_attn)(void* out, const void* q, int q_stride, c
   KGE_REQUIRE(hd == 64 || hd == 128, "kge_paged_attn: head_dim=%d unsupported (64, 128)", hd);
   if (!(max_q_len == 1 && H / KV <= 16))
     return paged_attn_prefill_tc((bf16*)out, (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-                                 max_blocks_per_seq, seq_lens, query_start_loc, B, max_q_len, H, KV, hd, block_size, scale, 0.f, nullptr, st);
+                                 max_blocks_per_seq, seq_lens, query_start_loc, B, max_q_len, H, KV, hd, block_size, scale, softcap, sinks, st);
   if (hd == 64)
     return launch_attn<64>((bf16*)out, (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache,
                            block_table, max_blocks_per_seq, seq_lens, query_start_loc, B, max_q_len,
-                           max_seq_len, H, KV, block_size, scale, workspace, workspace_bytes, st);
+                           max_seq_len, H, KV, block_size, scale, workspace, workspace_bytes, softcap, sinks, st);
   if (hd == 128)
     return launch_attn<128>((bf16*)out, (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache,
                             block_table, max_blocks_per_seq, seq_lens, query_start_loc, B, max_q_len,
-                            max_seq_len, H, KV, block_size, scale, workspace, workspace_bytes, st);
+                            max_seq_len, H, KV, block_size, scale, workspace, workspace_bytes, softcap, sinks, st);
   kge::set_error("kge_paged_attn: head_dim=%d unsupported (64, 128)", hd);
   return -1;
+}
+// whether a pure decode step with these sizes reaches a kernel that has the cap and the sinks
+bool paged_attn_extras_decode_ok(int B, int H, int KV, int hd, int block_size) {
+  return (hd == 64 || hd == 128) && H % KV == 0 && H / KV <= 16 && tunable(TUN_ATTN_TMA) && block_size >= 32 &&
+         (block_size & (block_size - 1)) == 0 && decode_tma_supported(B, KV, block_size);
+}
+}  // namespace KGE_ELT_NS
+}  // namespace kge
+
+extern "C" int KGE_API(kge_paged_attn)(void* out, const void* q, int q_stride, const void* k_cache,
+                              const void* v_cache, const int32_t* block_table, int max_blocks_per_seq,
+                              const int32_t* seq_lens, const int32_t* query_start_loc, int B, int T,
+                              int max_q_len, int max_seq_len, int H, int KV, int hd, int block_size,
+                              float scale, void* workspace, int64_t workspace_bytes, void* stream) {
+  return paged_attn_extras(out, q, q_stride, k_cache, v_cache, block_table, max_blocks_per_seq, seq_lens, query_start_loc, B, T, max_q_len,
+                           max_seq_len, H, KV, hd, block_size, scale, 0.f, nullptr, workspace, workspace_bytes, stream);
 }
 
 #ifndef KGE_HALF      // bfloat16 only: one scratch array per library image
@@ -529,9 +552,9 @@ extern "C" int kge_paged_attn_decode_noalloc(void* out, const void* q, int q_str
   if (hd == 64)
     return launch_attn<64>((bf16*)out, (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
                            max_blocks_per_seq, seq_lens, query_start_loc, B, 1, max_seq_len, H, KV, block_size, scale,
-                           ws, kNoAllocScratchBytes, st);
+                           ws, kNoAllocScratchBytes, 0.f, nullptr, st);
   return launch_attn<128>((bf16*)out, (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
                           max_blocks_per_seq, seq_lens, query_start_loc, B, 1, max_seq_len, H, KV, block_size, scale,
-                          ws, kNoAllocScratchBytes, st);
+                          ws, kNoAllocScratchBytes, 0.f, nullptr, st);
 }
 #endif

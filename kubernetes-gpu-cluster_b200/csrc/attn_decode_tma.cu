@@ -89,6 +89,18 @@ __device__ __forceinline__ uint32_t swz_kv(int key, int c /* 16-byte chunk of th
   return (uint32_t)((c >> 3) * (BN * 128) + key * 128 + (((c & 7) ^ (key & 7)) << 4));
 }
 
+// A score in units of log 2: scale_log2 * s, or - with a soft cap (cap_log2 = cap * log2(e) > 0, cap_in2 = 2 log2(e) scale / cap) -
+// cap_log2 * tanh(scale * s / cap) as 1 - 2 / (e^(2y) + 1), absolute error of a few 1e-7.  Decoding streams keys from HBM:
+// the extra special-function work hides behind the loads.
+__device__ __forceinline__ float score_log2(float s, float scale_log2, float cap_in2, float cap_log2) {
+  if (cap_log2 > 0.f) return fmaf(-2.f * cap_log2, __fdividef(1.f, exp2f(fminf(s * cap_in2, 100.f)) + 1.f), cap_log2);
+  return s * scale_log2;
+}
+// exp(sink logit of `head`) relative to the row's reference maximum (units of log 2); 0 without sinks
+__device__ __forceinline__ float sink_term(const float* sinks, int head, float basem) {
+  return sinks ? exp2f(sinks[head] * 1.4426950408889634f - basem) : 0.f;
+}
+
 // grid (splits, KV, B); 160 threads: warps 0-3 compute, warp 4 = TMA producer.
 template <int HD>
 __global__ void __launch_bounds__(160, 2)
@@ -96,7 +108,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                        const bf16* __restrict__ q, int q_stride, const int32_t* __restrict__ block_table, int max_blocks,
                        const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ qsl, int H, int KV, int bs_shift,
-                       float scale_log2) {
+                       float scale_log2, float cap_in2, float cap_log2, const float* __restrict__ sinks) {
   constexpr int CH = HD / 8;
   constexpr uint32_t TILE = BN * HD * 2;                  // one K or V tile
   constexpr uint32_t Q_BYTES = 16 * HD * 2;
@@ -212,10 +224,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int k0 = key_base + j * 8;
-        s[j][0] = (k0 < kv_len) ? s[j][0] * scale_log2 : -INFINITY;
-        s[j][1] = (k0 + 1 < kv_len) ? s[j][1] * scale_log2 : -INFINITY;
-        s[j][2] = (k0 < kv_len) ? s[j][2] * scale_log2 : -INFINITY;
-        s[j][3] = (k0 + 1 < kv_len) ? s[j][3] * scale_log2 : -INFINITY;
+        s[j][0] = (k0 < kv_len) ? score_log2(s[j][0], scale_log2, cap_in2, cap_log2) : -INFINITY;
+        s[j][1] = (k0 + 1 < kv_len) ? score_log2(s[j][1], scale_log2, cap_in2, cap_log2) : -INFINITY;
+        s[j][2] = (k0 < kv_len) ? score_log2(s[j][2], scale_log2, cap_in2, cap_log2) : -INFINITY;
+        s[j][3] = (k0 + 1 < kv_len) ? score_log2(s[j][3], scale_log2, cap_in2, cap_log2) : -INFINITY;
         mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
         mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
       }
@@ -282,6 +294,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
       }
       const int head = kvh * G + r;
       if (nsplit == 1) {
+        ll += sink_term(sinks, head, basem);
         out[(int64_t)qrow * H * HD + head * HD + c] = f2bf(ll > 0.f ? acc / ll : 0.f);
       } else {
         const int64_t pi = ((int64_t)b * H + head) * nsplit + split;
@@ -314,6 +327,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
             acc += __ldcg(part_o + (p0 + sidx) * HD + c) * sc;
             ll += __ldcg(part_ml + (p0 + sidx) * 2 + 1) * sc;
           }
+          ll += sink_term(sinks, kvh * G + r, basem);
           out[(int64_t)qrow * H * HD + (kvh * G + r) * HD + c] = f2bf(ll > 0.f ? acc / ll : 0.f);
         }
         if (tid == 0) g_split_arrivals[b * KV + kvh] = 0;      // ready for the next launch
@@ -342,7 +356,8 @@ attn_decode_tma_persistent_kernel(const __grid_constant__ CUtensorMap tm_k, cons
                                   bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                                   const bf16* __restrict__ q, int q_stride, const int32_t* __restrict__ block_table, int max_blocks,
                                   const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ qsl, int B, int H, int KV,
-                                  int bs_shift, float scale_log2, int slots /* partial slots per (request, head) */, int min_chunk) {
+                                  int bs_shift, float scale_log2, int slots /* partial slots per (request, head) */, int min_chunk,
+                                  float cap_in2, float cap_log2, const float* __restrict__ sinks) {
   constexpr int CH = HD / 8;
   constexpr uint32_t TILE = BN * HD * 2;
   constexpr uint32_t Q_BYTES = 16 * HD * 2;
@@ -524,10 +539,10 @@ attn_decode_tma_persistent_kernel(const __grid_constant__ CUtensorMap tm_k, cons
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int k0 = key_base + j * 8;
-        s[j][0] = (k0 < kv_len) ? s[j][0] * scale_log2 : -INFINITY;
-        s[j][1] = (k0 + 1 < kv_len) ? s[j][1] * scale_log2 : -INFINITY;
-        s[j][2] = (k0 < kv_len) ? s[j][2] * scale_log2 : -INFINITY;
-        s[j][3] = (k0 + 1 < kv_len) ? s[j][3] * scale_log2 : -INFINITY;
+        s[j][0] = (k0 < kv_len) ? score_log2(s[j][0], scale_log2, cap_in2, cap_log2) : -INFINITY;
+        s[j][1] = (k0 + 1 < kv_len) ? score_log2(s[j][1], scale_log2, cap_in2, cap_log2) : -INFINITY;
+        s[j][2] = (k0 < kv_len) ? score_log2(s[j][2], scale_log2, cap_in2, cap_log2) : -INFINITY;
+        s[j][3] = (k0 + 1 < kv_len) ? score_log2(s[j][3], scale_log2, cap_in2, cap_log2) : -INFINITY;
         mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
         mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
       }
@@ -597,6 +612,7 @@ attn_decode_tma_persistent_kernel(const __grid_constant__ CUtensorMap tm_k, cons
         }
         const int head = kvh * G + r;
         if (nsplit == 1) {
+          ll += sink_term(sinks, head, basem);
           out[(int64_t)qrow * H * HD + head * HD + c] = f2bf(ll > 0.f ? acc / ll : 0.f);
         } else {
           const int64_t pi = ((int64_t)b * H + head) * slots + split;
@@ -652,7 +668,10 @@ attn_decode_tma_persistent_kernel(const __grid_constant__ CUtensorMap tm_k, cons
               const float sc = exp2f(ml[sidx * 2] - basem);
               acc += v[k] * sc;
               ll += ml[sidx * 2 + 1] * sc;
-              if (sidx == nsplit - 1) out[(int64_t)qrow * H * HD + (kvh * G + r) * HD + c] = f2bf(ll > 0.f ? acc / ll : 0.f);
+              if (sidx == nsplit - 1) {
+                ll += sink_term(sinks, kvh * G + r, basem);
+                out[(int64_t)qrow * H * HD + (kvh * G + r) * HD + c] = f2bf(ll > 0.f ? acc / ll : 0.f);
+              }
             }
           }
         }
@@ -679,7 +698,8 @@ template <int HD> constexpr int smem_bytes() {
 template <int HD>
 static int launch_decode_tma(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc, const int32_t* bt, int max_blocks,
                              const int32_t* sl, const int32_t* qsl, int B, int H, int KV, int bs, int ns, float scale_log2,
-                             float* part_o, float* part_ml, void* ws, int64_t ws_bytes, int max_seq_len, cudaStream_t st) {
+                             float* part_o, float* part_ml, void* ws, int64_t ws_bytes, int max_seq_len, float cap_in2, float cap_log2,
+                             const float* sinks, cudaStream_t st) {
   int bs_shift = 0;
   while ((1 << bs_shift) < bs) ++bs_shift;
   CUtensorMap tk, tv;
@@ -713,7 +733,7 @@ static int launch_decode_tma(bf16* out, const bf16* q, int q_stride, const bf16*
         float* po = (float*)ws;
         float* pml = po + (int64_t)B * H * slots * HD;
         KGE_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(160), smem, st, tk, tv, out, po, pml, q, q_stride, bt, max_blocks, sl, qsl, B, H, KV,
-                               bs_shift, scale_log2, (int)slots, min_chunk));
+                               bs_shift, scale_log2, (int)slots, min_chunk, cap_in2, cap_log2, sinks));
         return 0;
       }
     }
@@ -721,7 +741,7 @@ static int launch_decode_tma(bf16* out, const bf16* q, int q_stride, const bf16*
   auto kern = adt::attn_decode_tma_kernel<HD>;
   KGE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, adt::smem_bytes<HD>()));
   KGE_CUDA_OK(launch_pdl(kern, dim3(ns, KV, B), dim3(160), adt::smem_bytes<HD>(), st, tk, tv, out, part_o, part_ml, q, q_stride, bt,
-                         max_blocks, sl, qsl, H, KV, bs_shift, scale_log2));
+                         max_blocks, sl, qsl, H, KV, bs_shift, scale_log2, cap_in2, cap_log2, sinks));
   return 0;
 }
 
@@ -729,12 +749,13 @@ bool decode_tma_supported(int B, int KV, int bs) { return bs >= 8 && (int64_t)B 
 
 int paged_attn_decode_tma(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc, const int32_t* bt, int max_blocks,
                           const int32_t* sl, const int32_t* qsl, int B, int H, int KV, int hd, int bs, int ns, float scale_log2,
-                          float* part_o, float* part_ml, void* ws, int64_t ws_bytes, int max_seq_len, cudaStream_t st) {
+                          float* part_o, float* part_ml, void* ws, int64_t ws_bytes, int max_seq_len, float cap_in2, float cap_log2,
+                          const float* sinks, cudaStream_t st) {
   if (hd == 128)
     return launch_decode_tma<128>(out, q, q_stride, kc, vc, bt, max_blocks, sl, qsl, B, H, KV, bs, ns, scale_log2, part_o, part_ml, ws, ws_bytes,
-                                  max_seq_len, st);
+                                  max_seq_len, cap_in2, cap_log2, sinks, st);
   return launch_decode_tma<64>(out, q, q_stride, kc, vc, bt, max_blocks, sl, qsl, B, H, KV, bs, ns, scale_log2, part_o, part_ml, ws, ws_bytes,
-                               max_seq_len, st);
+                               max_seq_len, cap_in2, cap_log2, sinks, st);
 }
 
 }  // namespace KGE_ELT_NS

@@ -19,10 +19,13 @@ using namespace kge;
 
 namespace kge {
 inline namespace b16 {
-// attn_tc.cu: tcgen05 attention over query chunks (64- and 128-wide heads, bfloat16), optional soft cap and sink logits
-int paged_attn_prefill_tc(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc, const int32_t* bt, int max_blocks,
-                          const int32_t* sl, const int32_t* qsl, int B, int max_q_len, int H, int KV, int hd, int bs, float scale, float softcap,
-                          const float* sinks, cudaStream_t st);
+// attn.cu: the paged attention of the Llama family (tcgen05 kernel for steps with query chunks, TMA-staged split-KV
+// kernels for decode steps; 64- and 128-wide heads, bfloat16) with an optional soft cap and sink logits
+int paged_attn_extras(void* out, const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                      int max_blocks_per_seq, const int32_t* seq_lens, const int32_t* query_start_loc, int B, int T, int max_q_len,
+                      int max_seq_len, int H, int KV, int hd, int block_size, float scale, float softcap, const float* sinks, void* workspace,
+                      int64_t workspace_bytes, void* stream);
+bool paged_attn_extras_decode_ok(int B, int H, int KV, int hd, int block_size);
 }
 
 namespace {
@@ -272,6 +275,18 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
     e->moe_pw = (float*)aalloc(np, 4); e->moe_cw = (float*)aalloc(np, 4);
     if (!e->moe_hidden || !e->moe_out || !e->moe_goff || !e->moe_ptok || !e->moe_pdest || !e->moe_cexp || !e->moe_pw || !e->moe_cw) return fail(b.err);
   }
+  {
+    // split-KV scratch of the TMA-staged decode attention, for attention mixers whose heads it takes
+    int64_t need = 0;
+    for (auto& h : s.hybrid)
+      if (h.mixer == HybridLayerSpec::ATTENTION && !e->f32 && (h.dim == 64 || h.dim == 128) && h.vdim == h.dim)
+        need = std::max<int64_t>(need, kge_attn_workspace_bytes(Rm, h.heads, h.dim, e->cfg.max_model_len));
+    if (need > 0) {
+      e->ws_attn_bytes = need;
+      e->ws_attn = aalloc(need, 1);
+      if (!e->ws_attn) return fail("attention workspace allocation failed: " + b.err);
+    }
+  }
   e->d_out = (int32_t*)aalloc(Rm, 4);
   e->lp_vals = (float*)aalloc((int64_t)Rm * 21, 4);
   e->lp_ids = (int32_t*)aalloc((int64_t)Rm * 21, 4);
@@ -443,12 +458,15 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       for (int t = 0; t < T; ++t) keys += hm.pos[t] + 1;
       // steps with prompt pieces, 64- / 128-wide heads, bfloat16: the tcgen05 kernel of the Llama family (TMA-staged K/V
       // tiles, S and O in TMEM) with the cap and the sinks; everything else: the mma.sync / per-row kernels
-      const bool tc = !e->f32 && !decode_only && (h.dim == 64 || h.dim == 128) && h.vdim == h.dim && ldp % 8 == 0 && (bs & (bs - 1)) == 0 &&
-                      h.heads / h.kv_heads <= 128 && ((uintptr_t)e->pbuf & 15) == 0;
+      const bool tc = !e->f32 && (h.dim == 64 || h.dim == 128) && h.vdim == h.dim && ldp % 8 == 0 && (bs & (bs - 1)) == 0 &&
+                      h.heads / h.kv_heads <= 128 && ((uintptr_t)e->pbuf & 15) == 0 &&
+                      (!decode_only || (e->ws_attn && paged_attn_extras_decode_ok(B, h.heads, h.kv_heads, h.dim, bs)));
+      // a decode step may be replayed as a graph while its contexts grow: sized for the longest context its block-table stride holds
+      const int max_seq_bound = decode_only ? max_blocks * bs : 0;
       HFWD(decode_only ? C_ATT_DEC : C_ATT_GEN, (decode_only ? keys : (double)T) * h.kv_heads * (h.dim + h.vdim) * es + (double)T * h.heads * (h.dim + h.vdim) * es,
            2.0 * keys * h.heads * (h.dim + h.vdim),
-           tc ? paged_attn_prefill_tc((bf16*)e->mixbuf, (const bf16*)e->pbuf, ldp, (const bf16*)L.kc, (const bf16*)L.vc, m.btab, max_blocks, m.seq_lens, m.qsl,
-                                      B, aa.max_q, h.heads, h.kv_heads, h.dim, bs, h.scale, h.softcap, L.sinks, st)
+           tc ? paged_attn_extras(e->mixbuf, e->pbuf, ldp, L.kc, L.vc, m.btab, max_blocks, m.seq_lens, m.qsl, B, T, aa.max_q, std::max(max_seq_bound, 1),
+                                  h.heads, h.kv_heads, h.dim, bs, h.scale, h.softcap, L.sinks, e->ws_attn, e->ws_attn_bytes, st)
               : attn_bias_chunk(aa, st));
       DENSE(e->obuf1, d, e->mixbuf, ko, L.o, T, ACT_NONE);
       add_src(e->obuf1, d, 1.f);
