@@ -176,6 +176,14 @@ def route(h, router, bias, top):
     return picks
 
 
+def route_margins(h, router, bias, top):
+    """Per token: by how much the last chosen logit leads the first one left out (inf when every expert is chosen)."""
+    z, _ = torch.sort(h @ router.T + bias, dim=-1, descending=True)
+    if top >= z.shape[1]:
+        return torch.full((h.shape[0],), math.inf, dtype=DT)
+    return z[:, top - 1] - z[:, top]
+
+
 def moe(h, W, prefix, f):
     out = torch.zeros_like(h)
     for t, (order, w) in enumerate(route(h, W[prefix + "router"], W[prefix + "router.b"], f["router"]["top"])):
@@ -191,20 +199,26 @@ def sub(W, prefix):
     return {k[len(prefix):]: v for k, v in W.items() if k.startswith(prefix)}
 
 
-def forward(cfg, W, tokens, return_layers=False):
-    """Logits [T, vocab] of one sequence (float64), optionally the residual stream after every layer."""
+def forward(cfg, W, tokens, return_layers=False, return_margins=False):
+    """Logits [T, vocab] of one sequence (float64); optionally the residual stream after every layer, or per token the
+    smallest routing margin over the layers (a 16-bit engine may choose another expert where it is tiny)."""
     eps = cfg["norm"]["eps"]
     x = W["embed"][torch.tensor(tokens)]
     layers = []
+    margins = torch.full((len(tokens),), math.inf, dtype=DT)
     for i, L in enumerate(cfg["layers"]):
         p = f"l{L.get('weights_of', i)}."
         x = x + sink_attention(layer_norm(x, W[p + "norm1"], eps), sub(W, p + "mix."), L["mixer"], eps)
         if L["mlp"]:
-            x = x + moe(layer_norm(x, W[p + "norm2"], eps), W, p + "mlp.", L["mlp"])
+            h2 = layer_norm(x, W[p + "norm2"], eps)
+            margins = torch.minimum(margins, route_margins(h2, W[p + "mlp.router"], W[p + "mlp.router.b"], L["mlp"]["router"]["top"]))
+            x = x + moe(h2, W, p + "mlp.", L["mlp"])
         layers.append(x)
     z = layer_norm(x, W["final.norm"], eps) @ W["head"].T
     cap = cfg.get("logit_softcap") or 0.0
     logits = cap * torch.tanh(z / cap) if cap > 0 else z
+    if return_margins:
+        return logits, margins
     return (logits, layers) if return_layers else logits
 
 

@@ -33,12 +33,30 @@ def run_pieces(llm, rid, tokens, pieces):
     return np.concatenate(out)
 
 
-def check(got, want, dtype, what=""):
+def check(got, want, dtype, what="", margins=None):
+    """Row-wise error against the oracle, relative to the logits' size.  bfloat16 engines form the router's logits from
+    rounded activations: where the oracle's own choice hangs on a margin below 0.05 (`margins`, per token) another expert
+    may be chosen, so such rows are left out, and the rows after the first of them, which see that token through the
+    attention of later layers, get a wider bound (still far below what a lost key, a wrong position or a wrong expert
+    weight costs: 0.3 and more).  The float32 runs of the same cases are the sharp ones."""
     want = want.numpy() if isinstance(want, torch.Tensor) else want
     scale = np.sqrt((want ** 2).mean())
     err = np.sqrt(((got - want) ** 2).mean(-1)) / scale
-    lim = 2e-4 if dtype == "float32" else 4e-2
-    assert err.max() < lim, f"{what}: worst row {err.argmax()} is {err.max():.3g} of the logits' size (limit {lim})"
+    lim = np.full(len(err), 2e-4 if dtype == "float32" else 4e-2)
+    if dtype != "float32" and margins is not None:
+        close = np.asarray(margins) < 0.05
+        assert close.mean() < 0.5, f"{what}: {close.sum()} of {len(close)} rows hang on a close routing call"
+        if close.any():
+            lim[int(np.argmax(close)):] = 0.15
+            lim[close] = np.inf
+    worst = int(np.argmax(err / lim))
+    assert (err < lim).all(), f"{what}: row {worst} is {err[worst]:.3g} of the logits' size (limit {lim[worst]:.3g})"
+
+
+def oracle(cfg, W, toks):
+    """Logits and routing margins as numpy arrays."""
+    lg, mg = og.forward(cfg, W, toks, return_margins=True)
+    return lg.numpy(), mg.numpy()
 
 
 def prompt(cfg, n, seed=1):
@@ -77,7 +95,8 @@ def test_mechanism_alone(kge, tmp_path, mech, dtype):
     llm = make_engine(kge, tmp_path, cfg, W, dtype)
     got = run_pieces(llm, 0, toks, [45])
     llm.close()
-    check(got, og.forward(cfg, W, toks), dtype, mech)
+    want, mg = oracle(cfg, W, toks)
+    check(got, want, dtype, mech, mg)
 
 
 FULL = dict(n_layers=4, weights_of={2: 0, 3: 1}, mlps=(True, True, True, True))
@@ -88,12 +107,12 @@ def test_prefill_decode_and_pieces_agree_with_the_oracle(kge, tmp_path, dtype):
     cfg = og.make_config(**FULL)
     W = og.make_weights(cfg, seed=5)
     toks = prompt(cfg, 75)
-    want = og.forward(cfg, W, toks)
+    want, mg = oracle(cfg, W, toks)
     llm = make_engine(kge, tmp_path, cfg, W, dtype)
     for rid, pieces in enumerate([[75], [30] + [1] * 45, [1] * 75, [2, 3, 17, 2, 31, 5, 2, 2, 9, 2], [23, 2, 24, 26], [47, 2, 1, 1, 24]]):
         got = run_pieces(llm, rid, toks, pieces)
         llm.trace_end(rid)
-        check(got, want, dtype, f"pieces {pieces[:6]}")
+        check(got, want, dtype, f"pieces {pieces[:6]}", mg)
     llm.close()
 
 
@@ -132,7 +151,7 @@ def test_mixed_batches_of_unequal_requests(kge, tmp_path, dtype):
     cfg = og.make_config(**FULL)
     W = og.make_weights(cfg, seed=7)
     P = {0: prompt(cfg, 61, 10), 1: prompt(cfg, 9, 11), 2: prompt(cfg, 40, 12), 3: prompt(cfg, 1, 13)}
-    want = {r: og.forward(cfg, W, t).numpy() for r, t in P.items()}
+    want = {r: oracle(cfg, W, t) for r, t in P.items()}
     # each step: (request, number of tokens); prompt pieces beside single tokens, requests pausing and resuming
     steps = [[(0, 19), (1, 1), (3, 1)], [(1, 1), (2, 2), (0, 2)], [(0, 20), (1, 1)], [(2, 18), (1, 1), (0, 1)], [(1, 5), (2, 1)],
              [(0, 1), (2, 1)], [(0, 18), (2, 18)]]
@@ -153,7 +172,7 @@ def test_mixed_batches_of_unequal_requests(kge, tmp_path, dtype):
     llm.close()
     for r in P:
         assert at[r] == len(P[r])
-        check(np.concatenate(got[r]), want[r], dtype, f"request {r}")
+        check(np.concatenate(got[r]), want[r][0], dtype, f"request {r}", want[r][1])
 
 
 def test_pages_and_slots_are_used_again(kge, tmp_path):
@@ -206,6 +225,7 @@ def test_far_keys_and_page_borders_with_peaked_scores(kge, tmp_path, dtype, dim)
     assert float((og.forward(cfg, nosink, toks[:40]) - want[:40]).abs().max()) > 0.2
     llm = make_engine(kge, tmp_path, cfg, W, dtype, bs=16)
     check(run_pieces(llm, 0, toks, [330]), want, dtype, "whole")
+    llm.trace_end(0)
     check(run_pieces(llm, 1, toks[:100], [15, 1, 1, 1, 14, 2, 30, 1, 1, 34]), want[:100], dtype, "pieces and single tokens across page borders")
     llm.trace_end(1)
     got = np.concatenate([run_pieces(llm, 2, toks[:290], [290]), run_pieces(llm, 2, toks[290:], [1] * 40)])
@@ -234,11 +254,11 @@ def test_long_prompt_tensor_core_kernels(kge, tmp_path):
                          weights_of={1: 0})
     W = og.make_weights(cfg, seed=15)
     toks = prompt(cfg, 290, 32)
-    want = og.forward(cfg, W, toks)
+    want, mg = oracle(cfg, W, toks)
     llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", bs=64)
     got = np.concatenate([run_pieces(llm, 0, toks[:150], [150]), run_pieces(llm, 0, toks[150:260], [3, 45, 2, 60]), run_pieces(llm, 0, toks[260:], [1] * 30)])
     llm.close()
-    check(got, want, "bfloat16")
+    check(got, want, "bfloat16", "", mg)
 
 
 def test_experts_with_many_routed_rows(kge, tmp_path):
@@ -248,14 +268,14 @@ def test_experts_with_many_routed_rows(kge, tmp_path):
     cfg = og.make_config(n_layers=1, width=64, experts=6, top=2, expert_ff=64, shared_ff=128, expert_limit=0.4, shared_limit=0.3)
     W = silence_attention(og.make_weights(cfg, seed=16))
     toks = prompt(cfg, 300, 33)
-    want = og.forward(cfg, W, toks)
+    want, mg = oracle(cfg, W, toks)
     loose = copy.deepcopy(cfg)
     loose["layers"][0]["mlp"]["expert"]["limit"] = 50.0
-    assert float((og.forward(loose, W, toks) - want).abs().max()) > 0.1
+    assert float(np.abs(og.forward(loose, W, toks).numpy() - want).max()) > 0.1
     llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", bs=64)
-    check(run_pieces(llm, 0, toks, [300]), want, "bfloat16", "one step")
+    check(run_pieces(llm, 0, toks, [300]), want, "bfloat16", "one step", mg)
     llm.trace_end(0)
-    check(run_pieces(llm, 1, toks, [280, 7, 13]), want, "bfloat16", "pieces")
+    check(run_pieces(llm, 1, toks, [280, 7, 13]), want, "bfloat16", "pieces", mg)
     llm.close()
 
 
@@ -317,9 +337,9 @@ def test_greedy_generation_through_the_scheduler(kge, tmp_path, dtype):
         for k, g in enumerate(got):       # teacher-forced: a different choice must be a near-tie of the oracle
             lg = og.forward(cfg, W, toks)[-1]
             best = int(torch.argmax(lg))
-            if g != best:
+            if g != best:      # the samplers read 16-bit logits rows: two logits within their spacing tie
                 gap = float(lg[best] - lg[g])
-                assert gap < (1e-3 if dtype == "float32" else 0.15), f"token {k}: chose {g}, oracle {best} leads by {gap}"
+                assert gap < (2.0 ** -7 * max(1.0, float(lg[best].abs())) if dtype == "float32" else 0.15), f"token {k}: chose {g}, oracle {best} leads by {gap}"
             toks.append(g)
 
 
