@@ -270,6 +270,10 @@ int embed_f32(float* res, const int32_t* ids, const void* table, int T, int d, i
   return 0;
 }
 
+template <bool LN>      // rows of up to 8192 columns held in registers (defined with the layer norm below)
+static bool norm_vec(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, float out_scale, int elt, cudaStream_t st,
+                     cudaError_t* ce);
+
 template <typename E>
 __global__ void rmsnorm_f32in_kernel(E* y, const float* x, const int32_t* rows, const E* w, int d, float eps, float offset, float out_scale) {
   pdl_launch_dependents();
@@ -286,11 +290,74 @@ __global__ void rmsnorm_f32in_kernel(E* y, const float* x, const int32_t* rows, 
 int rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, float out_scale, int elt,
                   cudaStream_t st) {
   if (R <= 0) return 0;
-  cudaError_t ce = elt == KGE_ELT_F32
+  cudaError_t ce;
+  if (norm_vec<false>(y, x, rows, w, R, d, eps, offset, out_scale, elt, st, &ce)) { KGE_CUDA_OK(ce); return 0; }
+  ce = elt == KGE_ELT_F32
       ? launch_pdl(rmsnorm_f32in_kernel<float>, dim3(R), dim3(256), 0, st, (float*)y, x, rows, (const float*)w, d, eps, offset, out_scale)
       : launch_pdl(rmsnorm_f32in_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, st, (__nv_bfloat16*)y, x, rows, (const __nv_bfloat16*)w, d, eps, offset, out_scale);
   KGE_CUDA_OK(ce);
   return 0;
+}
+
+// Both norms for rows of up to 8192 columns (a multiple of 4): the row is read once, as float4, and stays in registers for
+// the statistics (layer norm: mean first, then the squared deviations) and the output (four values per store).
+constexpr int NV_MAX = 8;
+__device__ __forceinline__ float4 ldw4(const float* w) { return *reinterpret_cast<const float4*>(w); }
+__device__ __forceinline__ float4 ldw4(const __nv_bfloat16* w) {
+  const uint2 u = *reinterpret_cast<const uint2*>(w);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void st4(float* y, float4 v) { *reinterpret_cast<float4*>(y) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* y, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u; u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(y) = u;
+}
+template <typename E, bool LN>
+__global__ void __launch_bounds__(256) norm_f32in_vec_kernel(E* y, const float* x, const int32_t* rows, const E* w, int d, float eps, float offset, float out_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[33];
+  const int r = blockIdx.x, nvec = d >> 2;
+  const float* src = x + (int64_t)(rows ? rows[r] : r) * d;
+  float4 v[NV_MAX];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV_MAX; ++i) {
+    const int c = threadIdx.x + i * 256;
+    v[i] = c < nvec ? *reinterpret_cast<const float4*>(src + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (LN) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  float mean = 0.f;
+  if (LN) { mean = block_sum(s, red) / (float)d; __syncthreads(); }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV_MAX; ++i) {
+    if (threadIdx.x + i * 256 < nvec) {
+      v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+      ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss); ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = out_scale / sqrtf(ss / (float)d + eps);
+#pragma unroll
+  for (int i = 0; i < NV_MAX; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      const float4 g = ldw4(w + 4 * c);
+      st4(y + (int64_t)r * d + 4 * c, make_float4(v[i].x * inv * (offset + g.x), v[i].y * inv * (offset + g.y), v[i].z * inv * (offset + g.z), v[i].w * inv * (offset + g.w)));
+    }
+  }
+}
+template <bool LN>
+static bool norm_vec(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float offset, float out_scale, int elt, cudaStream_t st,
+                     cudaError_t* ce) {
+  if (d % 4 || d > 4 * 256 * NV_MAX || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return false;
+  *ce = elt == KGE_ELT_F32
+      ? launch_pdl(norm_f32in_vec_kernel<float, LN>, dim3(R), dim3(256), 0, st, (float*)y, x, rows, (const float*)w, d, eps, offset, out_scale)
+      : launch_pdl(norm_f32in_vec_kernel<__nv_bfloat16, LN>, dim3(R), dim3(256), 0, st, (__nv_bfloat16*)y, x, rows, (const __nv_bfloat16*)w, d, eps, offset, out_scale);
+  return true;
 }
 
 // weight-only layer norm of an fp32 row: mean first, then the mean of the squared deviations (no cancellation)
@@ -313,7 +380,9 @@ __global__ void layernorm_f32in_kernel(E* y, const float* x, const int32_t* rows
 }
 int layernorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, float eps, float out_scale, int elt, cudaStream_t st) {
   if (R <= 0) return 0;
-  cudaError_t ce = elt == KGE_ELT_F32
+  cudaError_t ce;
+  if (norm_vec<true>(y, x, rows, w, R, d, eps, 0.f, out_scale, elt, st, &ce)) { KGE_CUDA_OK(ce); return 0; }
+  ce = elt == KGE_ELT_F32
       ? launch_pdl(layernorm_f32in_kernel<float>, dim3(R), dim3(256), 0, st, (float*)y, x, rows, (const float*)w, d, eps, out_scale)
       : launch_pdl(layernorm_f32in_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, st, (__nv_bfloat16*)y, x, rows, (const __nv_bfloat16*)w, d, eps, out_scale);
   KGE_CUDA_OK(ce);
@@ -334,9 +403,37 @@ __global__ void residual_combine_kernel(float* res, CombineArgs a, int64_t n, in
     res[i] += s;
   }
 }
+// four columns per thread: one float4 of the stream, one 8- or 16-byte piece of every source
+template <typename E>
+__global__ void residual_combine_vec_kernel(float* res, CombineArgs a, int64_t n4, int d4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / d4; const int c = (int)(i % d4) * 4;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < a.n; ++k) {
+      const float f = a.rscale[k] ? a.scale[k] * a.rscale[k][t * a.rs_stride[k]] : a.scale[k];
+      const float4 v = ldw4((const E*)a.src[k] + t * a.ld[k] + c);
+      s.x = fmaf(f, v.x, s.x); s.y = fmaf(f, v.y, s.y); s.z = fmaf(f, v.z, s.z); s.w = fmaf(f, v.w, s.w);
+    }
+    float4* dst = reinterpret_cast<float4*>(res) + i;
+    float4 o = *dst;
+    o.x += s.x; o.y += s.y; o.z += s.z; o.w += s.w;
+    *dst = o;
+  }
+}
 int residual_combine(float* res, const CombineArgs& a, int T, int d, int elt, cudaStream_t st) {
   if (T <= 0 || a.n <= 0) return 0;
   const int64_t n = (int64_t)T * d;
+  bool vec = d % 4 == 0 && (reinterpret_cast<uintptr_t>(res) & 15) == 0;
+  for (int k = 0; k < a.n; ++k) vec = vec && a.ld[k] % 4 == 0 && (reinterpret_cast<uintptr_t>(a.src[k]) & 15) == 0;
+  if (vec) {
+    const int grid4 = (int)std::min<int64_t>((n / 4 + 255) / 256, 148 * 16);
+    cudaError_t ce4 = elt == KGE_ELT_F32 ? launch_pdl(residual_combine_vec_kernel<float>, dim3(grid4), dim3(256), 0, st, res, a, n / 4, d / 4)
+                                         : launch_pdl(residual_combine_vec_kernel<__nv_bfloat16>, dim3(grid4), dim3(256), 0, st, res, a, n / 4, d / 4);
+    KGE_CUDA_OK(ce4);
+    return 0;
+  }
   const int grid = (int)std::min<int64_t>((n + 255) / 256, 148 * 8);
   cudaError_t ce = elt == KGE_ELT_F32 ? launch_pdl(residual_combine_kernel<float>, dim3(grid), dim3(256), 0, st, res, a, n, d)
                                       : launch_pdl(residual_combine_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, res, a, n, d);

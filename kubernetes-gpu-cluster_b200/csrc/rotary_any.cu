@@ -96,12 +96,102 @@ __global__ void __launch_bounds__(256) rotary_norm_kvwrite_kernel(RotaryArgs a) 
   }
 }
 
+// bfloat16, head size a multiple of 8, 16-byte aligned rows and caches: a token's q and k rows are read ONCE, eight values
+// (16 bytes) per piece, and stay in registers for the sums of squares and for norm, rotation and the stores (16 bytes each).
+// Up to RV_MAX pieces per thread: (H + G) * dim <= 256 * 8 * RV_MAX.
+constexpr int RV_MAX = 4;
+__global__ void __launch_bounds__(256) rotary_norm_kvwrite_vec_kernel(RotaryArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  typedef __nv_bfloat16 E;
+  extern __shared__ float cs[];                 // [rot_dims / 2] cos, then sin (multiplier applied)
+  __shared__ float red[33];
+  const int t = blockIdx.x, half = a.rot_dims >> 1, nq = a.H * a.dim, nk = a.G * a.dim, pq = nq >> 3, pall = (nq + nk) >> 3;
+  const int pos = a.positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double s, c;
+    sincos((double)pos * a.freq[i], &s, &c);
+    cs[i] = (float)c * a.mult;
+    cs[half + i] = (float)s * a.mult;
+  }
+  E* q = (E*)a.q + (int64_t)t * a.ldq;
+  const E* k = (const E*)a.k + (int64_t)t * a.ldk;
+  uint4 raw[RV_MAX];
+  float ssq = 0.f, ssk = 0.f;
+#pragma unroll
+  for (int i = 0; i < RV_MAX; ++i) {
+    const int p = threadIdx.x + i * 256;
+    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (p < pall) {
+      raw[i] = p < pq ? *reinterpret_cast<const uint4*>(q + 8 * p) : *reinterpret_cast<const uint4*>(k + 8 * (p - pq));
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h2[j]); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); }
+      if (p < pq) ssq += ss; else ssk += ss;
+    }
+  }
+  float inv_q = 1.f, inv_k = 1.f;
+  if (a.q_norm_w) { inv_q = 1.f / sqrtf(block_sum(ssq, red) / (float)nq + a.eps); __syncthreads(); }
+  if (a.k_norm_w) inv_k = 1.f / sqrtf(block_sum(ssk, red) / (float)nk + a.eps);
+  __syncthreads();
+  const int64_t slot = a.slots ? a.slots[t] : -1;
+  const int64_t blk = slot >= 0 ? slot / a.block_size : 0, off = slot >= 0 ? slot % a.block_size : 0;
+#pragma unroll
+  for (int i = 0; i < RV_MAX; ++i) {
+    const int p = threadIdx.x + i * 256;
+    if (p >= pall) continue;
+    const bool isq = p < pq;
+    const int col = isq ? 8 * p : 8 * (p - pq), head = col / a.dim, d0 = col % a.dim;
+    const int64_t cache_off = ((blk * a.G + head) * a.block_size + off) * a.dim + d0;
+    if (!isq && slot >= 0 && a.v_cache && !a.v) *reinterpret_cast<uint4*>((E*)a.v_cache + cache_off) = raw[i];     // values = the raw key projection
+    const E* nw = (const E*)(isq ? a.q_norm_w : a.k_norm_w);
+    uint4 wraw = make_uint4(0u, 0u, 0u, 0u);
+    if (nw) wraw = *reinterpret_cast<const uint4*>(nw + col);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+    const float inv = isq ? inv_q : inv_k;
+    uint4 outv;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&outv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(h2[j]);
+      f.x *= inv; f.y *= inv;
+      if (nw) { const float2 g = __bfloat1622float2(w2[j]); f.x *= g.x; f.y *= g.y; }
+      const int d = d0 + 2 * j;
+      if (d + 1 < a.rot_dims) {
+        const float c = cs[d >> 1], s = cs[half + (d >> 1)];
+        const float ru = f.x * c - f.y * s, rv = f.y * c + f.x * s;
+        f.x = ru; f.y = rv;
+      }
+      o2[j] = __floats2bfloat162_rn(f.x, f.y);
+    }
+    if (isq) *reinterpret_cast<uint4*>(q + col) = outv;
+    else if (slot >= 0 && a.k_cache) *reinterpret_cast<uint4*>((E*)a.k_cache + cache_off) = outv;
+  }
+  // a value projection of its own
+  if (slot >= 0 && a.v_cache && a.v) {
+    const E* v = (const E*)a.v + (int64_t)t * a.ldv;
+    E* vc = (E*)a.v_cache;
+    for (int c = threadIdx.x; c < a.G * a.vdim; c += blockDim.x) {
+      const int g = c / a.vdim, d = c % a.vdim;
+      vc[((blk * a.G + g) * a.block_size + off) * a.vdim + d] = v[c];
+    }
+  }
+}
+
 int rotary_norm_kvwrite(const RotaryArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
   KGE_REQUIRE(a.q && a.k && a.positions && a.H > 0 && a.G > 0 && a.dim > 0 && a.rot_dims >= 0 && a.rot_dims <= a.dim && a.rot_dims % 2 == 0 &&
               (a.rot_dims == 0 || a.freq), "rotary_norm_kvwrite: bad arguments");
   KGE_REQUIRE(a.v || a.vdim == a.dim, "rotary_norm_kvwrite: values taken from the keys need vdim = dim");
   const size_t smem = (size_t)std::max(a.rot_dims, 2) * 4;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (a.elt == KGE_ELT_BF16 && a.dim % 8 == 0 && a.ldq % 8 == 0 && a.ldk % 8 == 0 && (a.H + a.G) * a.dim <= 256 * 8 * RV_MAX && al16(a.q) && al16(a.k) &&
+      al16(a.k_cache) && al16(a.v_cache) && al16(a.q_norm_w) && al16(a.k_norm_w) && (a.v || a.vdim == a.dim)) {
+    KGE_CUDA_OK(launch_pdl(rotary_norm_kvwrite_vec_kernel, dim3(a.T), dim3(256), smem, st, a));
+    return 0;
+  }
   cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(rotary_norm_kvwrite_kernel<float>, dim3(a.T), dim3(256), smem, st, a)
                                         : launch_pdl(rotary_norm_kvwrite_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), smem, st, a);
   KGE_CUDA_OK(ce);

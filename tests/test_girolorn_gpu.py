@@ -261,6 +261,44 @@ def test_long_prompt_tensor_core_kernels(kge, tmp_path):
     check(got, want, "bfloat16", "", mg)
 
 
+@pytest.mark.parametrize("shape", [(4, 4, 128, 64), (6, 2, 64, 64), (8, 1, 64, 32), (2, 1, 128, 128)])
+def test_tensor_core_head_sizes(kge, tmp_path, shape):
+    """bfloat16, 64-token pages, attention alone with scores at the cap and sinks of real weight, at the head sizes and
+    group sizes (1, 2, 3 and 8 query heads per key/value head) that the tcgen05 prompt kernel and the TMA-staged decode
+    kernels take; prompt steps, pieces beside nothing else, then decoding over a page border."""
+    heads, kv, dim, rot = shape
+    cfg = og.make_config(n_layers=2, width=64, heads=heads, kv_heads=kv, dim=dim, rot_dims=rot, scale=2.0 * (12 / dim) ** 0.5, softcap=10.0,
+                         mlps=(False, False), weights_of={1: 0})
+    W = og.make_weights(cfg, seed=23)
+    W["l0.mix.sink"] = torch.linspace(-1.0, 3.0, heads, dtype=og.DT)
+    toks = prompt(cfg, 230, 34)
+    want = og.forward(cfg, W, toks)
+    nosink = dict(W)
+    nosink["l0.mix.sink"] = torch.full_like(W["l0.mix.sink"], -50.0)
+    assert float((og.forward(cfg, nosink, toks[:30]) - want[:30]).abs().max()) > 0.2
+    llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", bs=64, tokens=1024)
+    check(run_pieces(llm, 0, toks, [230]), want, "bfloat16", "whole")
+    llm.trace_end(0)
+    got = np.concatenate([run_pieces(llm, 1, toks[:180], [61, 3, 2, 64, 50]), run_pieces(llm, 1, toks[180:], [1] * 50)])
+    check(got, want, "bfloat16", "pieces, then decoding")
+    # two requests decoding side by side (one far longer than the other) and a third that brings a prompt piece
+    a, b = prompt(cfg, 150, 35), prompt(cfg, 9, 36)
+    wa, wb = og.forward(cfg, W, a).numpy(), og.forward(cfg, W, b).numpy()
+    llm.trace_add(2, a[:140])
+    llm.trace_add(3, b[:3])
+    llm.trace_step([(2, 140, []), (3, 3, [])])
+    ga, gb = [], []
+    for i in range(6):
+        llm.trace_add(2, a[140 + i:141 + i])
+        llm.trace_add(3, b[3 + i:4 + i])
+        lg = llm.trace_step([(2, 1, [0]), (3, 1, [0])])
+        ga.append(lg[0])
+        gb.append(lg[1])
+    llm.close()
+    check(np.stack(ga), wa[140:146], "bfloat16", "long request of a decode batch")
+    check(np.stack(gb), wb[3:9], "bfloat16", "short request of a decode batch")
+
+
 def test_experts_with_many_routed_rows(kge, tmp_path):
     """A prompt long enough that the routed rows are made contiguous per expert and run as one tensor-core GEMM pair per
     expert (bfloat16; expert width a multiple of 64); the same prompt fed in short pieces takes the grouped kernel.
