@@ -267,7 +267,7 @@ def test_tensor_core_head_sizes(kge, tmp_path, shape):
     group sizes (1, 2, 3 and 8 query heads per key/value head) that the tcgen05 prompt kernel and the TMA-staged decode
     kernels take; prompt steps, pieces beside nothing else, then decoding over a page border."""
     heads, kv, dim, rot = shape
-    cfg = og.make_config(n_layers=2, width=64, heads=heads, kv_heads=kv, dim=dim, rot_dims=rot, scale=2.0 * (12 / dim) ** 0.5, softcap=10.0,
+    cfg = og.make_config(n_layers=2, width=64, heads=heads, kv_heads=kv, dim=dim, rot_dims=rot, scale=1.4 * (12 / dim) ** 0.5, softcap=10.0,
                          mlps=(False, False), weights_of={1: 0})
     W = og.make_weights(cfg, seed=23)
     W["l0.mix.sink"] = torch.linspace(-1.0, 3.0, heads, dtype=og.DT)
