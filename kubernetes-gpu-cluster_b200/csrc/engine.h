@@ -102,6 +102,8 @@ struct kge_engine {
   float *res32 = nullptr, *gates32 = nullptr, *logits32 = nullptr, *state = nullptr, *mo32 = nullptr;
   void *hx = nullptr, *pbuf = nullptr, *ubuf = nullptr, *mixbuf = nullptr, *obuf1 = nullptr, *obuf2 = nullptr, *ffbuf = nullptr;
   void *moe_hidden = nullptr, *moe_out = nullptr, *hsel = nullptr, *moe_xperm = nullptr, *moe_operm = nullptr;
+  int32_t* moe_tile_group = nullptr;         // expert of every 256-row tile of the padded routed rows (prompt steps)
+  int64_t moe_rows_padded = 0;               // rows the routed-row buffers hold
   int32_t* moe_goff_host = nullptr;          // pinned copy of the experts' row offsets (prompt steps size one GEMM per expert from it)
   int32_t *moe_goff = nullptr, *moe_ptok = nullptr, *moe_pdest = nullptr, *moe_cexp = nullptr;
   float *moe_pw = nullptr, *moe_cw = nullptr;

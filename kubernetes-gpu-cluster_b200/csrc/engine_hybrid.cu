@@ -26,6 +26,9 @@ int paged_attn_extras(void* out, const void* q, int q_stride, const void* k_cach
                       int max_seq_len, int H, int KV, int hd, int block_size, float scale, float softcap, const float* sinks, void* workspace,
                       int64_t workspace_bytes, void* stream);
 bool paged_attn_extras_decode_ok(int B, int H, int KV, int hd, int block_size);
+// gemm_tc.cu: one tcgen05 launch over row groups padded to 256 (the experts of a prompt step)
+int gemm_grouped(void* y, const void* x, const void* w, int T, int N, int K, int groups, const int32_t* tile_group, int glu, float glu_alpha,
+                 float glu_limit, cudaStream_t st);
 }
 
 namespace {
@@ -263,7 +266,11 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   e->logits = (bf16*)aalloc((int64_t)std::max(Rm, Tm) * e->ld_logits, 2);
   e->state = (float*)aalloc((int64_t)Rm * e->slot_stride, 4);
   if (max_top > 0) {
-    const int64_t np = (int64_t)Tm * max_top;
+    const int64_t np0 = (int64_t)Tm * max_top;
+    const int64_t np = e->f32 ? np0 : (np0 / 256 + max_E + 1) * 256;      // bfloat16: room for groups padded to 256 rows
+    e->moe_rows_padded = np;
+    e->moe_tile_group = (int32_t*)aalloc(np / 256 + 1, 4);
+    if (!e->moe_tile_group) return fail(b.err);
     e->moe_hidden = aalloc(np * max_eff, es);
     e->moe_out = aalloc(np * d, es);
     if (!e->f32) {
@@ -520,30 +527,25 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       ra.score_fn = w_out ? 2 : 0; ra.renorm = false;
       ra.group_off = e->moe_goff; ra.perm_token = e->moe_ptok; ra.perm_weight = e->moe_pw; ra.perm_dest = e->moe_pdest;
       ra.choice_expert = e->moe_cexp; ra.choice_weight = e->moe_cw; ra.elt = elt;
+      const int np = T * h.top;
+      // bfloat16 prompt steps with enough routed rows: groups padded to 256 rows for the grouped tensor-core GEMMs
+      const int np_pad = (np / 256 + h.experts + 1) * 256;
+      const bool grouped = !e->f32 && !decode_only && np >= 512 && h.expert_ff % 64 == 0 && d % 8 == 0 && e->moe_xperm && np_pad <= e->moe_rows_padded;
+      if (grouped) { ra.pad = 256; ra.rows_padded = np_pad; ra.tile_group = e->moe_tile_group; }
       HFWD(C_MOE, Td * es + (double)h.experts * d * es, 2.0 * Td * h.experts, moe_route(ra, st));
       ++e->launches;
-      const int np = T * h.top;
       const double wexp = (double)std::min(h.experts, np) * h.expert_ff * d * es;      // weights of the experts that are touched (at most)
-      if (!e->f32 && !decode_only && np >= 512 && h.expert_ff % 64 == 0 && d % 8 == 0 && e->moe_xperm) {
-        // prompt steps: the routed rows are made contiguous per expert and every expert runs the tensor-core GEMMs
-        // (gated front half with SiLU*mul in the epilogue, then down) on its own rows; the row counts come to the host
-        // once per layer - a few microseconds beside milliseconds of expert work
+      if (grouped) {
+        // prompt steps: every expert's routed rows, padded to a multiple of 256, are contiguous; ONE tensor-core launch
+        // runs the gated front half of all experts (the pair formed in the epilogue) and one the down projections; each
+        // 256-row tile takes its expert's weights from the stacked tensors.  Nothing comes back to the host.
         const int eff = h.expert_ff;
-        HFWD(C_MOE, (double)np * d * 4, 0, moe_gather_rows(e->moe_xperm, e->hx, d, e->moe_ptok, w_out ? nullptr : e->moe_pw, np, d, st));
-        KGE_CUDA_OK(cudaMemcpyAsync(e->moe_goff_host, e->moe_goff, (size_t)(h.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
-        KGE_CUDA_OK(cudaStreamSynchronize(st));
-        for (int x = 0; x < h.experts; ++x) {
-          const int off = e->moe_goff_host[x], cnt = e->moe_goff_host[x + 1] - off;
-          if (cnt <= 0) continue;
-          const uint8_t* wgu = (const uint8_t*)L.e_gate + (int64_t)x * 2 * eff * d * 2;
-          const uint8_t* wdn = (const uint8_t*)L.e_down + (int64_t)x * d * eff * 2;
-          HFWD(cnt <= 256 ? C_GEMM_S : C_MOE, 2.0 * (2.0 * eff * d + (double)cnt * (d + eff)), 4.0 * cnt * (double)eff * d,
-               clamped ? kge_gemm_clamped_glu_bf16(at(e->moe_hidden, (int64_t)off * eff), at(e->moe_xperm, (int64_t)off * d), wgu, cnt, eff, d, 1.702f, h.expert_limit, nullptr, 0, st)
-                       : kge_gemm_silu_gate_ws_bf16(at(e->moe_hidden, (int64_t)off * eff), at(e->moe_xperm, (int64_t)off * d), wgu, cnt, eff, d, nullptr, 0, st));
-          HFWD(cnt <= 256 ? C_GEMM_S : C_MOE, 2.0 * ((double)eff * d + (double)cnt * (d + eff)), 2.0 * cnt * (double)eff * d,
-               kge_gemm_bf16(at(e->moe_operm, (int64_t)off * d), at(e->moe_hidden, (int64_t)off * eff), wdn, nullptr, cnt, d, eff, 0, nullptr, 0, st));
-        }
-        HFWD(C_MOE, (double)np * d * 4, 0, moe_scatter_rows(e->moe_out, e->moe_operm, e->moe_pdest, np, d, st));
+        HFWD(C_MOE, (double)np_pad * d * 4, 0, moe_gather_rows(e->moe_xperm, e->hx, d, e->moe_ptok, w_out ? nullptr : e->moe_pw, np_pad, d, st));
+        HFWD(C_MOE, 2.0 * (2.0 * h.experts * eff * d + (double)np_pad * (d + eff)), 4.0 * np * (double)eff * d,
+             gemm_grouped(e->moe_hidden, e->moe_xperm, L.e_gate, np_pad, eff, d, h.experts, e->moe_tile_group, clamped ? 1 : 0, 1.702f, h.expert_limit, st));
+        HFWD(C_MOE, 2.0 * ((double)h.experts * eff * d + (double)np_pad * (d + eff)), 2.0 * np * (double)eff * d,
+             gemm_grouped(e->moe_operm, e->moe_hidden, L.e_down, np_pad, d, eff, h.experts, e->moe_tile_group, -1, 0.f, 0.f, st));
+        HFWD(C_MOE, (double)np * d * 4, 0, moe_scatter_rows(e->moe_out, e->moe_operm, e->moe_pdest, np_pad, d, st));
       } else {
       LinearArgs g;      // experts' gated front half on the gathered, weighted rows
       g.x = e->hx; g.ldx = d; g.w = L.e_gate; g.w2 = L.e_up; g.y = e->moe_hidden; g.ldy = h.expert_ff; g.T = np; g.N = h.expert_ff; g.K = d;

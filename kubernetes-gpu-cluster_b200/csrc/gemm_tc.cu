@@ -119,6 +119,10 @@ struct GemmParams {
   unsigned long long* trace; // phase timestamps, 16 per CTA (tools/gemm_trace.py); null outside that tool
   int glu = 0;               // gated pair: 0 silu(gate) * up; 1 clamped: g = min(gate, limit), u = clamp(up, +-limit), g * sigmoid(alpha g) * (u + 1)
   float glu_alpha = 0.f, glu_limit = 0.f;
+  // grouped rows (mixture of experts): token rows come in groups padded to multiples of 256, tile_group[i] names the weight
+  // slice of rows [256 i, 256 (i + 1)), and slice g starts at weight row g * group_rows of the stacked weight tensor
+  const int32_t* tile_group = nullptr;
+  int group_rows = 0;
 };
 
 // epilogue activation of the plain projection: 0 none, 1 relu, 3 exact (erf) gelu; 2 marks the gated pair internally
@@ -303,34 +307,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       int stage = 0; uint32_t phase = 0;
       const bool hint = p.l2_hints != 0;
       const uint64_t pol_w = l2_policy(false), pol_x = l2_policy(true);
-      auto load_a = [&](int st, int kb, int m_tile) {
+      auto load_a = [&](int st, int kb, int m_tile, int woff) {
         const uint32_t a_dst = smem_base + st * STAGE_BYTES;
         if (PAIR && hint) {
           if (GATED) {
-            tma_load_2d_cg2_hint(a_dst, &tmap_w, lead_full(st), kb * BLK_K, m_tile * 64, pol_w);
-            tma_load_2d_cg2_hint(a_dst + 64 * BLK_K * 2, &tmap_w, lead_full(st), kb * BLK_K, p.N + m_tile * 64, pol_w);
+            tma_load_2d_cg2_hint(a_dst, &tmap_w, lead_full(st), kb * BLK_K, woff + m_tile * 64, pol_w);
+            tma_load_2d_cg2_hint(a_dst + 64 * BLK_K * 2, &tmap_w, lead_full(st), kb * BLK_K, woff + p.N + m_tile * 64, pol_w);
           } else {
-            tma_load_2d_cg2_hint(a_dst, &tmap_w, lead_full(st), kb * BLK_K, m_tile * BLK_M, pol_w);
+            tma_load_2d_cg2_hint(a_dst, &tmap_w, lead_full(st), kb * BLK_K, woff + m_tile * BLK_M, pol_w);
           }
         } else if (PAIR) {
           if (GATED) {
-            tma_load_2d_cg2(a_dst, &tmap_w, lead_full(st), kb * BLK_K, m_tile * 64);
-            tma_load_2d_cg2(a_dst + 64 * BLK_K * 2, &tmap_w, lead_full(st), kb * BLK_K, p.N + m_tile * 64);
+            tma_load_2d_cg2(a_dst, &tmap_w, lead_full(st), kb * BLK_K, woff + m_tile * 64);
+            tma_load_2d_cg2(a_dst + 64 * BLK_K * 2, &tmap_w, lead_full(st), kb * BLK_K, woff + p.N + m_tile * 64);
           } else {
-            tma_load_2d_cg2(a_dst, &tmap_w, lead_full(st), kb * BLK_K, m_tile * BLK_M);
+            tma_load_2d_cg2(a_dst, &tmap_w, lead_full(st), kb * BLK_K, woff + m_tile * BLK_M);
           }
         } else if (hint) {
           if (GATED) {
-            tma_load_2d_hint(a_dst, &tmap_w, full_bar(st), kb * BLK_K, m_tile * 64, pol_w);
-            tma_load_2d_hint(a_dst + 64 * BLK_K * 2, &tmap_w, full_bar(st), kb * BLK_K, p.N + m_tile * 64, pol_w);
+            tma_load_2d_hint(a_dst, &tmap_w, full_bar(st), kb * BLK_K, woff + m_tile * 64, pol_w);
+            tma_load_2d_hint(a_dst + 64 * BLK_K * 2, &tmap_w, full_bar(st), kb * BLK_K, woff + p.N + m_tile * 64, pol_w);
           } else {
-            tma_load_2d_hint(a_dst, &tmap_w, full_bar(st), kb * BLK_K, m_tile * BLK_M, pol_w);
+            tma_load_2d_hint(a_dst, &tmap_w, full_bar(st), kb * BLK_K, woff + m_tile * BLK_M, pol_w);
           }
         } else if (GATED) {
-          tma_load_2d(a_dst, &tmap_w, full_bar(st), kb * BLK_K, m_tile * 64);                          // gate rows
-          tma_load_2d(a_dst + 64 * BLK_K * 2, &tmap_w, full_bar(st), kb * BLK_K, p.N + m_tile * 64);   // up rows
+          tma_load_2d(a_dst, &tmap_w, full_bar(st), kb * BLK_K, woff + m_tile * 64);                          // gate rows
+          tma_load_2d(a_dst + 64 * BLK_K * 2, &tmap_w, full_bar(st), kb * BLK_K, woff + p.N + m_tile * 64);   // up rows
         } else {
-          tma_load_2d(a_dst, &tmap_w, full_bar(st), kb * BLK_K, m_tile * BLK_M);
+          tma_load_2d(a_dst, &tmap_w, full_bar(st), kb * BLK_K, woff + m_tile * BLK_M);
         }
       };
       // the barrier that counts a stage's bytes: own (48 KB) or, PAIR, the leader's for both CTAs (2 x 32 KB)
@@ -354,10 +358,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         SegIter peek = segments();
         if (peek.next(w, kb0, kb1)) {            // the first segment's first stages (a later segment's are loaded in the loop)
           const int m_tile = m_tile_of(w);
-          pre = min(STAGES, kb1 - kb0);
+          pre = p.tile_group ? 0 : min(STAGES, kb1 - kb0);      // which weights a tile needs is the previous kernel's output
           for (int i = 0; i < pre; ++i) {
             expect(i);
-            load_a(i, kb0 + i, m_tile);
+            load_a(i, kb0 + i, m_tile, 0);
             if (i == 0) trace_stamp(p, 13);
           }
         }
@@ -369,13 +373,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       bool first_seg = true;
       while (it.next(w, kb0, kb1)) {
         const int n_tile = w % p.n_tiles, m_tile = m_tile_of(w);
+        const int woff = p.tile_group ? p.tile_group[(n_tile * TOKN) >> 8] * p.group_rows : 0;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (first_seg && kb - kb0 < pre) {
             load_b(stage, kb, n_tile);
           } else {
             mbar_wait(empty_bar(stage), phase ^ 1);
             expect(stage);
-            load_a(stage, kb, m_tile);
+            load_a(stage, kb, m_tile, woff);
             load_b(stage, kb, n_tile);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -1361,6 +1366,34 @@ extern "C" int KGE_GEMM_GLU_NAME(void* y, const void* x, const void* w_gate_up, 
   KGE_REQUIRE(limit > 0.f, "kge_gemm_clamped_glu_bf16: limit must be positive");
   return gemm_gated(y, x, w_gate_up, T, f, K, 1, alpha, limit, workspace, workspace_bytes, stream);
 }
+
+namespace kge {
+inline namespace KGE_ELT_NS {
+// Grouped rows (the experts of a mixture, prompt steps): x [T, K] holds every group's rows padded to a multiple of 256,
+// w stacks `groups` weight matrices ([N, K] each, or [2f, K] = [gate | up] with glu >= 0), tile_group (device, T / 256
+// entries) names the matrix of every 256 rows.  y [T, N] (or [T, f]).  One launch for all groups, T > 256.
+// glu: -1 plain projection, 0 silu(gate) * up, 1 the clamped pair.
+int gemm_grouped(void* y, const void* x, const void* w, int T, int N, int K, int groups, const int32_t* tile_group, int glu, float glu_alpha,
+                 float glu_limit, cudaStream_t st) {
+  const bool gated = glu >= 0;
+  KGE_REQUIRE(y && x && w && tile_group && groups > 0, "gemm_grouped: null pointer");
+  KGE_REQUIRE(T > 256 && T % 256 == 0 && N > 0 && K > 0 && K % 8 == 0 && (!gated || N % 64 == 0), "gemm_grouped: T=%d N=%d K=%d", T, N, K);
+  KGE_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_grouped: x and w must be 16-byte aligned");
+  const GemmPlan g = plan_gemm(T, N, K, gated ? 64 : BLK_M);
+  KGE_REQUIRE(!g.ws && g.splits == 1 && 256 % g.tokn == 0, "gemm_grouped: internal: unexpected plan");
+  GemmParams p;
+  p.y = (bf16*)y; p.bias = nullptr; p.T = T; p.N = N; p.K = K; p.act = gated ? 2 : 0;
+  p.glu = gated ? glu : 0; p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
+  p.l2_hints = tunable(TUN_GEMM_L2_HINTS); p.trace = g_gemm_trace; p.ws_count = nullptr; p.ws_part = nullptr;
+  p.m_tiles = g.m_tiles; p.n_tiles = g.n_tiles; p.splits = g.splits; p.kb_total = g.kb_total; p.kb_per_split = g.kb_per_split;
+  p.tile_group = tile_group; p.group_rows = gated ? 2 * N : N;
+  CUtensorMap tw, tx;
+  if (int rc = make_tmap(&tw, w, (int64_t)groups * p.group_rows, K, gated ? 64 : BLK_M)) return rc;
+  if (int rc = make_tmap(&tx, x, T, K, gemm_uses_pair(g) ? 128 : g.tokn)) return rc;
+  return gated ? dispatch_gemm<true>(g, tw, tx, p, st) : dispatch_gemm<false>(g, tw, tx, p, st);
+}
+}  // namespace KGE_ELT_NS
+}  // namespace kge
 
 extern "C" int KGE_GEMM_GATE_NAME(void* y, const void* x, const void* w_gate_up, int T, int f, int K, void* stream) {
   return KGE_GEMM_GATE_WS_NAME(y, x, w_gate_up, T, f, K, nullptr, 0, stream);

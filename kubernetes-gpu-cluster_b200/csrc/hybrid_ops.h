@@ -165,6 +165,10 @@ struct MoeRouteArgs {
   int T = 0, d = 0, E = 0, top = 1, score_fn = 0; bool renorm = false;
   int32_t* group_off = nullptr; int32_t* perm_token = nullptr; float* perm_weight = nullptr; int32_t* perm_dest = nullptr;
   int32_t* choice_expert = nullptr; float* choice_weight = nullptr;     // scratch [T * top] each
+  // pad > 1: every expert's rows start at a multiple of `pad` (group_off holds the padded offsets; perm_* have rows_padded
+  // entries, -1 in perm_token / perm_dest marks a row without a pair), and tile_group [rows_padded / pad] names the expert
+  // of every tile of `pad` rows - what the grouped tensor-core GEMM reads
+  int pad = 0, rows_padded = 0; int32_t* tile_group = nullptr;
   int elt = KGE_ELT_BF16;
 };
 int moe_route(const MoeRouteArgs& a, cudaStream_t st);

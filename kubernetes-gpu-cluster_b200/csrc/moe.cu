@@ -76,10 +76,24 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(MoeRouteArgs a) {
   __syncthreads();
   if (threadIdx.x == 0) {
     int off = 0;
-    for (int e = 0; e < a.E; ++e) { a.group_off[e] = off; cur[e] = off; off += cnt[e]; }
+    for (int e = 0; e < a.E; ++e) {
+      a.group_off[e] = off; cur[e] = off;
+      off += a.pad > 1 ? (cnt[e] + a.pad - 1) / a.pad * a.pad : cnt[e];
+    }
     a.group_off[a.E] = off;
   }
   __syncthreads();
+  if (a.pad > 1) {
+    // padded groups: rows that carry no pair are marked (the gather writes zeros there, the scatter skips them), and every
+    // tile of `pad` rows learns its expert; tiles beyond the last group compute on zero rows with the first expert's weights
+    for (int i = threadIdx.x; i < a.rows_padded; i += blockDim.x) { a.perm_token[i] = -1; a.perm_dest[i] = -1; a.perm_weight[i] = 0.f; }
+    for (int i = threadIdx.x; i < a.rows_padded / a.pad; i += blockDim.x) {
+      int e = 0;
+      while (e + 1 < a.E && i * a.pad >= a.group_off[e + 1]) ++e;
+      a.tile_group[i] = i * a.pad < a.group_off[a.E] ? e : 0;
+    }
+    __syncthreads();
+  }
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const int p = atomicAdd(&cur[a.choice_expert[i]], 1);
     a.perm_token[p] = i / a.top;
@@ -92,7 +106,15 @@ __global__ void moe_gather_rows_kernel(__nv_bfloat16* xperm, const __nv_bfloat16
   pdl_launch_dependents();
   pdl_wait();
   const int p = blockIdx.x;
+  if (tok[p] < 0) {                              // a padding row of a group
+    for (int c = threadIdx.x; c < d; c += blockDim.x) xperm[(int64_t)p * d + c] = __float2bfloat16_rn(0.f);
+    return;
+  }
   const __nv_bfloat16* src = h + (int64_t)tok[p] * ldh;
+  if (!w && d % 8 == 0 && ldh % 8 == 0) {        // plain copy of the row, 16 bytes at a time
+    for (int c = threadIdx.x; c < d / 8; c += blockDim.x) reinterpret_cast<uint4*>(xperm + (int64_t)p * d)[c] = reinterpret_cast<const uint4*>(src)[c];
+    return;
+  }
   const float s = w ? w[p] : 1.f;
   for (int c = threadIdx.x; c < d; c += blockDim.x) xperm[(int64_t)p * d + c] = __float2bfloat16_rn(s * __bfloat162float(src[c]));
 }
@@ -100,6 +122,11 @@ __global__ void moe_scatter_rows_kernel(__nv_bfloat16* out, const __nv_bfloat16*
   pdl_launch_dependents();
   pdl_wait();
   const int p = blockIdx.x;
+  if (dest[p] < 0) return;
+  if (d % 8 == 0) {
+    for (int c = threadIdx.x; c < d / 8; c += blockDim.x) reinterpret_cast<uint4*>(out + (int64_t)dest[p] * d)[c] = reinterpret_cast<const uint4*>(operm + (int64_t)p * d)[c];
+    return;
+  }
   for (int c = threadIdx.x; c < d; c += blockDim.x) out[(int64_t)dest[p] * d + c] = operm[(int64_t)p * d + c];
 }
 int moe_gather_rows(void* xperm, const void* h, int ldh, const int32_t* perm_token, const float* perm_weight, int np, int d, cudaStream_t st) {
@@ -116,6 +143,8 @@ int moe_scatter_rows(void* out, const void* operm, const int32_t* perm_dest, int
 int moe_route(const MoeRouteArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
   KGE_REQUIRE(a.E > 0 && a.top > 0 && a.top <= a.E && a.E <= 4096, "moe_route: %d experts, top %d", a.E, a.top);
+  KGE_REQUIRE(a.pad <= 1 || (a.tile_group && a.rows_padded % a.pad == 0 && a.rows_padded >= a.T * a.top + a.E * (a.pad - 1)),
+              "moe_route: padded groups need tile_group and %d rows or more", a.T * a.top + a.E * (a.pad - 1));
   cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(moe_score_kernel<float>, dim3(a.T), dim3(256), (size_t)a.E * 4, st, a)
                                         : launch_pdl(moe_score_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), (size_t)a.E * 4, st, a);
   KGE_CUDA_OK(ce);

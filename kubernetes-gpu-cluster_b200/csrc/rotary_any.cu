@@ -3,7 +3,7 @@
 // q and k projections, the write of the rotated keys into the paged cache, and the write of the values (a projection of
 // their own, or the un-normed, un-rotated key projection).  One block per token: sums of squares in fp32, the token's
 // cos / sin pairs once in shared memory (angle = position * frequency formed in double precision, so long contexts
-// lose nothing in the argument reduction), then every head reads them.
+// lose nothing: whole turns are removed in double, the remainder goes through the fp32 sine and cosine), then every head reads them.
 #include <math.h>
 
 #include <algorithm>
@@ -30,6 +30,13 @@ void rotary_frequencies(int dims, double base, double factor, double original, d
   }
 }
 
+// sin and cos of an angle formed in double precision: whole turns are taken off in double (three operations), the rest -
+// within [-pi, pi], exact to an fp32 rounding - goes through the fp32 functions
+__device__ __forceinline__ void sincos_reduced(double ang, float* s, float* c) {
+  const double turns = rint(ang * 0.15915494309189535);
+  sincosf((float)fma(-turns, 6.283185307179586, ang), s, c);
+}
+
 template <typename E>
 __global__ void __launch_bounds__(256) rotary_norm_kvwrite_kernel(RotaryArgs a) {
   pdl_launch_dependents();
@@ -39,10 +46,10 @@ __global__ void __launch_bounds__(256) rotary_norm_kvwrite_kernel(RotaryArgs a) 
   const int t = blockIdx.x, half = a.rot_dims >> 1, nq = a.H * a.dim, nk = a.G * a.dim;
   const int pos = a.positions[t];
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    double s, c;
-    sincos((double)pos * a.freq[i], &s, &c);
-    cs[i] = (float)c * a.mult;
-    cs[half + i] = (float)s * a.mult;
+    float s, c;
+    sincos_reduced((double)pos * a.freq[i], &s, &c);
+    cs[i] = c * a.mult;
+    cs[half + i] = s * a.mult;
   }
   E* q = (E*)a.q + (int64_t)t * a.ldq;
   const E* k = (const E*)a.k + (int64_t)t * a.ldk;
@@ -109,10 +116,10 @@ __global__ void __launch_bounds__(256) rotary_norm_kvwrite_vec_kernel(RotaryArgs
   const int t = blockIdx.x, half = a.rot_dims >> 1, nq = a.H * a.dim, nk = a.G * a.dim, pq = nq >> 3, pall = (nq + nk) >> 3;
   const int pos = a.positions[t];
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    double s, c;
-    sincos((double)pos * a.freq[i], &s, &c);
-    cs[i] = (float)c * a.mult;
-    cs[half + i] = (float)s * a.mult;
+    float s, c;
+    sincos_reduced((double)pos * a.freq[i], &s, &c);
+    cs[i] = c * a.mult;
+    cs[half + i] = s * a.mult;
   }
   E* q = (E*)a.q + (int64_t)t * a.ldq;
   const E* k = (const E*)a.k + (int64_t)t * a.ldk;
