@@ -525,6 +525,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       const bool w_out = h.route == HybridLayerSpec::ROUTE_SOFTMAX_TOP;      // the routing weight multiplies the expert's output (in the fp32 sum below)
       const bool clamped = h.glu == HybridLayerSpec::GLU_CLAMPED;
       ra.score_fn = w_out ? 2 : 0; ra.renorm = false;
+      if (L.s_sg) { ra.w_extra = L.s_sg; ra.extra_sigmoid = e->gates32; }      // the shared expert's per-token gate rides along, kept in fp32
       ra.group_off = e->moe_goff; ra.perm_token = e->moe_ptok; ra.perm_weight = e->moe_pw; ra.perm_dest = e->moe_pdest;
       ra.choice_expert = e->moe_cexp; ra.choice_weight = e->moe_cw; ra.elt = elt;
       const int np = T * h.top;
@@ -575,11 +576,6 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
           HFWD(T <= 256 ? C_GEMM_S : C_GEMM_L, gb, gf, linear_any(sg, st));
         }
         DENSE(e->obuf2, d, e->ffbuf, f, L.s_down, T, ACT_NONE);
-        if (L.s_sg) {        // one sigmoid gate per token, kept in fp32 and applied in the residual sum
-          LinearArgs a;
-          a.x = e->hx; a.ldx = d; a.w = L.s_sg; a.y = e->gates32; a.ldy = 1; a.T = T; a.N = 1; a.K = d; a.act = ACT_SIGMOID; a.elt = elt; a.out_f32 = true;
-          HFWD(C_MOE, Td * es, 2.0 * Td, linear_any(a, st));
-        }
       }
       // sum in a fixed order: mixer, the token's experts by choice, the shared expert
       for (int k = 0; k < h.top; ++k) {

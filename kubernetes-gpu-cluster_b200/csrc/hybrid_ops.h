@@ -162,6 +162,7 @@ inline int64_t mlstm_state_floats(int H, int dim, int vdim) { return (int64_t)H 
 // every permuted row), perm_weight [T * top], perm_dest [T * top] (row t * top + choice of the output buffer).
 struct MoeRouteArgs {
   const void* h = nullptr; int ldh = 0; const void* w_router = nullptr; const void* b_router = nullptr;
+  const void* w_extra = nullptr; float* extra_sigmoid = nullptr;      // one more row [d]: extra_sigmoid[t] = sigmoid(w_extra . h_t) (a per-token gate)
   int T = 0, d = 0, E = 0, top = 1, score_fn = 0; bool renorm = false;
   int32_t* group_off = nullptr; int32_t* perm_token = nullptr; float* perm_weight = nullptr; int32_t* perm_dest = nullptr;
   int32_t* choice_expert = nullptr; float* choice_weight = nullptr;     // scratch [T * top] each

@@ -9,8 +9,39 @@
 
 namespace kge {
 
-// One block per token: its eight warps share the experts' dot products (fp32, ascending d per lane, lanes summed by
-// shuffles - the same order whatever the launch holds), then one thread picks the top-k.
+// One lane's share of the dot product of two rows, 16 bytes per load where the rows allow (the same order of summation
+// for a row whatever the launch holds)
+__device__ __forceinline__ float dot_part(const __nv_bfloat16* h, const __nv_bfloat16* w, int d, int lane, bool vec) {
+  float acc = 0.f;
+  if (vec) {
+    for (int k = lane * 8; k < d; k += 256) {
+      const uint4 a = *reinterpret_cast<const uint4*>(h + k), b = *reinterpret_cast<const uint4*>(w + k);
+      const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(b2[j]); acc = fmaf(x.x, y.x, acc); acc = fmaf(x.y, y.y, acc); }
+    }
+  } else {
+    for (int k = lane; k < d; k += 32) acc = fmaf(__bfloat162float(h[k]), __bfloat162float(w[k]), acc);
+  }
+  return acc;
+}
+__device__ __forceinline__ float dot_part(const float* h, const float* w, int d, int lane, bool vec) {
+  float acc = 0.f;
+  if (vec) {
+    for (int k = lane * 4; k < d; k += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(h + k), b = *reinterpret_cast<const float4*>(w + k);
+      acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+    }
+  } else {
+    for (int k = lane; k < d; k += 32) acc = fmaf(h[k], w[k], acc);
+  }
+  return acc;
+}
+
+// One block per token: its eight warps share the experts' dot products (fp32, lanes summed by shuffles - the same order
+// whatever the launch holds) and, where asked, one more row whose sigmoid is a per-token gate; then the first warp picks
+// the top-k, each lane scanning its share of the scores.
 template <typename E>
 __global__ void __launch_bounds__(256) moe_score_kernel(MoeRouteArgs a) {
   pdl_launch_dependents();
@@ -18,13 +49,17 @@ __global__ void __launch_bounds__(256) moe_score_kernel(MoeRouteArgs a) {
   extern __shared__ float sc[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x;
   const E* h = (const E*)a.h + (int64_t)t * a.ldh;
-  for (int e = warp; e < a.E; e += 8) {
-    const E* w = (const E*)a.w_router + (int64_t)e * a.d;
-    float acc = 0.f;
-#pragma unroll 8
-    for (int k = lane; k < a.d; k += 32) acc = fmaf(ldf(h + k), ldf(w + k), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) sc[e] = a.b_router ? acc + ldf((const E*)a.b_router + e) : acc;
+  constexpr int per = 16 / (int)sizeof(E);
+  const bool vec = a.d % per == 0 && a.ldh % per == 0 && (reinterpret_cast<uintptr_t>(a.h) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.w_router) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(a.w_extra) & 15) == 0;
+  const int nrows = a.E + (a.w_extra ? 1 : 0);
+  for (int e = warp; e < nrows; e += 8) {
+    const E* w = e < a.E ? (const E*)a.w_router + (int64_t)e * a.d : (const E*)a.w_extra;
+    const float acc = warp_sum(dot_part(h, w, a.d, lane, vec));
+    if (lane == 0) {
+      if (e < a.E) sc[e] = a.b_router ? acc + ldf((const E*)a.b_router + e) : acc;
+      else a.extra_sigmoid[t] = 1.f / (1.f + expf(-acc));
+    }
   }
   __syncthreads();
   if (warp != 0) return;
@@ -41,26 +76,40 @@ __global__ void __launch_bounds__(256) moe_score_kernel(MoeRouteArgs a) {
     for (int e = lane; e < a.E; e += 32) sc[e] /= sum;
   }
   __syncwarp();
-  if (lane == 0) {
-    float total = 0.f;
-    for (int k = 0; k < a.top; ++k) {
-      int best = -1; float bv = -INFINITY;
-      for (int e = 0; e < a.E; ++e) {
-        bool taken = false;
-        for (int q = 0; q < k; ++q) taken |= a.choice_expert[(int64_t)t * a.top + q] == e;
-        if (!taken && sc[e] > bv) { bv = sc[e]; best = e; }
-      }
-      if (best < 0) { best = 0; for (int q = 0; q < k; ++q) if (a.choice_expert[(int64_t)t * a.top + q] == best) ++best; bv = 0.f; }   // scores that are not numbers
-      a.choice_expert[(int64_t)t * a.top + k] = best;
-      a.choice_weight[(int64_t)t * a.top + k] = bv;
-      total += bv;
+  int32_t* ce = a.choice_expert + (int64_t)t * a.top;
+  float* cw = a.choice_weight + (int64_t)t * a.top;
+  for (int k = 0; k < a.top; ++k) {
+    // the largest score not yet taken, the lower index on a tie; a taken score is marked -inf in shared memory
+    float bv = -INFINITY; int best = 0x7fffffff;
+    for (int e = lane; e < a.E; e += 32) { const float v = sc[e]; if (v > bv) { bv = v; best = e; } }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, best, off);
+      if (ov > bv || (ov == bv && oi < best)) { bv = ov; best = oi; }
     }
+    if (lane == 0) {
+      if (best == 0x7fffffff) {      // scores that are not numbers (or all taken): the lowest index not chosen yet, weight 0
+        best = 0;
+        for (bool again = true; again;) { again = false; for (int q = 0; q < k; ++q) if (ce[q] == best) { ++best; again = true; } }
+        bv = 0.f;
+      }
+      ce[k] = best; cw[k] = bv;
+      sc[best] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
     if (a.score_fn == 2) {          // softmax over the chosen logits only (the first choice holds the largest)
-      const float mx = a.choice_weight[(int64_t)t * a.top];
-      total = 0.f;
-      for (int k = 0; k < a.top; ++k) { const float p = expf(a.choice_weight[(int64_t)t * a.top + k] - mx); a.choice_weight[(int64_t)t * a.top + k] = p; total += p; }
-      for (int k = 0; k < a.top; ++k) a.choice_weight[(int64_t)t * a.top + k] /= total;
-    } else if (a.renorm) for (int k = 0; k < a.top; ++k) a.choice_weight[(int64_t)t * a.top + k] /= total;
+      const float mx = cw[0];
+      float total = 0.f;
+      for (int k = 0; k < a.top; ++k) { const float p = expf(cw[k] - mx); cw[k] = p; total += p; }
+      for (int k = 0; k < a.top; ++k) cw[k] /= total;
+    } else if (a.renorm) {
+      float total = 0.f;
+      for (int k = 0; k < a.top; ++k) total += cw[k];
+      for (int k = 0; k < a.top; ++k) cw[k] /= total;
+    }
   }
 }
 
