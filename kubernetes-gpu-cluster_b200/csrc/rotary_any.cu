@@ -123,14 +123,17 @@ __global__ void __launch_bounds__(256) rotary_norm_kvwrite_vec_kernel(RotaryArgs
   }
   E* q = (E*)a.q + (int64_t)t * a.ldq;
   const E* k = (const E*)a.k + (int64_t)t * a.ldk;
-  uint4 raw[RV_MAX];
+  uint4 raw[RV_MAX], wraw[RV_MAX];              // the norm weights travel with the rows: one memory round trip, not two
   float ssq = 0.f, ssk = 0.f;
+  const int64_t slot = a.slots ? a.slots[t] : -1;
 #pragma unroll
   for (int i = 0; i < RV_MAX; ++i) {
     const int p = threadIdx.x + i * 256;
-    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    raw[i] = wraw[i] = make_uint4(0u, 0u, 0u, 0u);
     if (p < pall) {
       raw[i] = p < pq ? *reinterpret_cast<const uint4*>(q + 8 * p) : *reinterpret_cast<const uint4*>(k + 8 * (p - pq));
+      const E* nw0 = (const E*)(p < pq ? a.q_norm_w : a.k_norm_w);
+      if (nw0) wraw[i] = *reinterpret_cast<const uint4*>(nw0 + (p < pq ? 8 * p : 8 * (p - pq)));
       const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
       float ss = 0.f;
 #pragma unroll
@@ -142,7 +145,6 @@ __global__ void __launch_bounds__(256) rotary_norm_kvwrite_vec_kernel(RotaryArgs
   if (a.q_norm_w) { inv_q = 1.f / sqrtf(block_sum(ssq, red) / (float)nq + a.eps); __syncthreads(); }
   if (a.k_norm_w) inv_k = 1.f / sqrtf(block_sum(ssk, red) / (float)nk + a.eps);
   __syncthreads();
-  const int64_t slot = a.slots ? a.slots[t] : -1;
   const int64_t blk = slot >= 0 ? slot / a.block_size : 0, off = slot >= 0 ? slot % a.block_size : 0;
 #pragma unroll
   for (int i = 0; i < RV_MAX; ++i) {
@@ -153,10 +155,8 @@ __global__ void __launch_bounds__(256) rotary_norm_kvwrite_vec_kernel(RotaryArgs
     const int64_t cache_off = ((blk * a.G + head) * a.block_size + off) * a.dim + d0;
     if (!isq && slot >= 0 && a.v_cache && !a.v) *reinterpret_cast<uint4*>((E*)a.v_cache + cache_off) = raw[i];     // values = the raw key projection
     const E* nw = (const E*)(isq ? a.q_norm_w : a.k_norm_w);
-    uint4 wraw = make_uint4(0u, 0u, 0u, 0u);
-    if (nw) wraw = *reinterpret_cast<const uint4*>(nw + col);
     const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
-    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw[i]);
     const float inv = isq ? inv_q : inv_k;
     uint4 outv;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&outv);
