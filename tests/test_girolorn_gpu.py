@@ -261,11 +261,12 @@ def test_long_prompt_tensor_core_kernels(kge, tmp_path):
     check(got, want, "bfloat16", "", mg)
 
 
-@pytest.mark.parametrize("shape", [(4, 4, 128, 64), (6, 2, 64, 64), (8, 1, 64, 32), (2, 1, 128, 128)])
+@pytest.mark.parametrize("shape", [(4, 4, 128, 64), (6, 2, 64, 64), (8, 1, 64, 32), (2, 1, 128, 128), (5, 1, 64, 16)])
 def test_tensor_core_head_sizes(kge, tmp_path, shape):
     """bfloat16, 64-token pages, attention alone with scores at the cap and sinks of real weight, at the head sizes and
-    group sizes (1, 2, 3 and 8 query heads per key/value head) that the tcgen05 prompt kernel and the TMA-staged decode
-    kernels take; prompt steps, pieces beside nothing else, then decoding over a page border."""
+    group sizes (1, 2, 3, 5 and 8 query heads per key/value head) that the tcgen05 prompt kernel and the TMA-staged decode
+    kernels take; prompt steps, pieces beside nothing else, decoding over a page border, a decode batch of unequal
+    contexts, and single tokens beside a prompt piece in one step."""
     heads, kv, dim, rot = shape
     cfg = og.make_config(n_layers=2, width=64, heads=heads, kv_heads=kv, dim=dim, rot_dims=rot, scale=1.4 * (12 / dim) ** 0.5, softcap=10.0,
                          mlps=(False, False), weights_of={1: 0})
@@ -294,9 +295,19 @@ def test_tensor_core_head_sizes(kge, tmp_path, shape):
         lg = llm.trace_step([(2, 1, [0]), (3, 1, [0])])
         ga.append(lg[0])
         gb.append(lg[1])
+    # one more token of the long request beside the first piece of a new prompt and a lone first token
+    c, d1 = prompt(cfg, 70, 37), prompt(cfg, 1, 38)
+    llm.trace_end(3)
+    llm.trace_add(2, a[146:147])
+    llm.trace_add(4, c[:66])
+    llm.trace_add(5, d1)
+    lg = llm.trace_step([(2, 1, [0]), (4, 66, list(range(66))), (5, 1, [0])])
     llm.close()
     check(np.stack(ga), wa[140:146], "bfloat16", "long request of a decode batch")
     check(np.stack(gb), wb[3:9], "bfloat16", "short request of a decode batch")
+    check(lg[:1], wa[146:147], "bfloat16", "a single token beside a prompt piece")
+    check(lg[1:67], og.forward(cfg, W, c).numpy()[:66], "bfloat16", "a prompt piece beside single tokens")
+    check(lg[67:], og.forward(cfg, W, d1).numpy(), "bfloat16", "a lone first token in a mixed step")
 
 
 def test_experts_with_many_routed_rows(kge, tmp_path):
@@ -345,15 +356,21 @@ def test_long_decoding(kge, tmp_path):
          experts=9, top=4, expert_ff=11, expert_limit=0.6, shared_ff=13, shared_limit=3.0, mlps=(True, False, True), weights_of={2: 0}, eps=1e-3,
          logit_softcap=3.0),
     dict(n_layers=1, heads=2, kv_heads=1, dim=7, rot_dims=4, expert_ff=5, shared=False),
+    dict(n_layers=2, vocab=67, width=42, heads=3, kv_heads=1, dim=14, rot_dims=10, experts=3, top=2, expert_ff=64, shared_ff=64),      # rows of 84 bytes: nothing is 16-byte aligned
+    dict(n_layers=2, vocab=72, width=44, heads=2, kv_heads=2, dim=16, rot_dims=16, experts=4, top=3, expert_ff=24, shared_ff=8, weights_of={1: 0}),
 ])
 def test_other_sizes(kge, tmp_path, sizes):
     cfg = og.make_config(**sizes)
     W = og.make_weights(cfg, seed=13)
     toks = prompt(cfg, 50, 60)
-    want = og.forward(cfg, W, toks)
+    want, mg = oracle(cfg, W, toks)
     llm = make_engine(kge, tmp_path, cfg, W, "float32")
     check(run_pieces(llm, 0, toks, [50]), want, "float32", "whole")
     check(run_pieces(llm, 1, toks, [13, 2, 1, 1, 1, 32]), want, "float32", "pieces")
+    llm.close()
+    llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", name="b")        # the same sizes through the 16-bit kernels and their fallbacks
+    check(run_pieces(llm, 0, toks, [50]), want, "bfloat16", "whole, bfloat16", mg)
+    check(run_pieces(llm, 1, toks, [13, 2, 1, 1, 1, 32]), want, "bfloat16", "pieces, bfloat16", mg)
     llm.close()
 
 
