@@ -115,12 +115,6 @@ __global__ void __launch_bounds__(256) rotary_norm_kvwrite_vec_kernel(RotaryArgs
   __shared__ float red[33];
   const int t = blockIdx.x, half = a.rot_dims >> 1, nq = a.H * a.dim, nk = a.G * a.dim, pq = nq >> 3, pall = (nq + nk) >> 3;
   const int pos = a.positions[t];
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    float s, c;
-    sincos_reduced((double)pos * a.freq[i], &s, &c);
-    cs[i] = c * a.mult;
-    cs[half + i] = s * a.mult;
-  }
   E* q = (E*)a.q + (int64_t)t * a.ldq;
   const E* k = (const E*)a.k + (int64_t)t * a.ldk;
   uint4 raw[RV_MAX], wraw[RV_MAX];              // the norm weights travel with the rows: one memory round trip, not two
@@ -141,10 +135,25 @@ __global__ void __launch_bounds__(256) rotary_norm_kvwrite_vec_kernel(RotaryArgs
       if (p < pq) ssq += ss; else ssk += ss;
     }
   }
+  // the token's cos / sin pairs, while the rows are on their way
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincos_reduced((double)pos * a.freq[i], &s, &c);
+    cs[i] = c * a.mult;
+    cs[half + i] = s * a.mult;
+  }
+  // both sums of squares in one pass over the block
   float inv_q = 1.f, inv_k = 1.f;
-  if (a.q_norm_w) { inv_q = 1.f / sqrtf(block_sum(ssq, red) / (float)nq + a.eps); __syncthreads(); }
-  if (a.k_norm_w) inv_k = 1.f / sqrtf(block_sum(ssk, red) / (float)nk + a.eps);
-  __syncthreads();
+  {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    ssq = warp_sum(ssq); ssk = warp_sum(ssk);
+    if (lane == 0) { red[wid] = ssq; red[8 + wid] = ssk; }
+    __syncthreads();
+    float tq = lane < 8 ? red[lane] : 0.f, tk = lane < 8 ? red[8 + lane] : 0.f;
+    tq = warp_sum(tq); tk = warp_sum(tk);
+    if (a.q_norm_w) inv_q = 1.f / sqrtf(tq / (float)nq + a.eps);
+    if (a.k_norm_w) inv_k = 1.f / sqrtf(tk / (float)nk + a.eps);
+  }
   const int64_t blk = slot >= 0 ? slot / a.block_size : 0, off = slot >= 0 ? slot % a.block_size : 0;
 #pragma unroll
   for (int i = 0; i < RV_MAX; ++i) {
