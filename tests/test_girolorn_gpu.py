@@ -398,6 +398,30 @@ def test_greedy_generation_through_the_scheduler(kge, tmp_path, dtype):
             toks.append(g)
 
 
+def test_greedy_generation_with_decode_graphs(kge, tmp_path):
+    """LLM.generate at a head size the TMA-staged decode kernels take (bfloat16, 64-token pages): after the prompts the
+    decode steps are captured as a CUDA graph and replayed while the contexts grow over a page border; every sampled token
+    must be the oracle's choice or a near-tie of it."""
+    cfg = og.make_config(n_layers=2, width=64, heads=4, kv_heads=2, dim=64, rot_dims=32, scale=0.35, softcap=9.0, experts=4, top=2, expert_ff=64,
+                         shared_ff=64, weights_of={1: 0})
+    W = og.make_weights(cfg, seed=24)
+    prompts = [prompt(cfg, n, 90 + n) for n in (57, 9)]
+    llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", bs=64, tokens=512, seqs=2, batched=64)
+    outs = llm.generate(prompts, kge.SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True))
+    llm.close()
+    for p, o in zip(prompts, outs):
+        got = o.outputs[0].token_ids
+        assert len(got) == 20
+        toks = list(p)
+        for k, g in enumerate(got):
+            lg = og.forward(cfg, W, toks)[-1]
+            best = int(torch.argmax(lg))
+            if g != best:
+                gap = float(lg[best] - lg[g])
+                assert gap < 0.2, f"token {k}: chose {g}, oracle {best} leads by {gap}"
+            toks.append(g)
+
+
 def test_trace_runner_command_line(kge, tmp_path):
     """bin/trace_run end to end on this design: pieces of two requests side by side, a request that ends and one that
     takes its pages, both number formats."""
